@@ -9,7 +9,7 @@ Every request also holds one state slot; each state entry has a float32 tensor
 [slots, *shape], zeroed when a request takes its slot (imparo-model/src/lib.rs:1951-1972).
 
 Arena layout per group: K [entries, pages, page_size, kv_heads*head_dim] and V the same with the value size
-(PagedKV.v_head_dim, the key size unless given).
+(PagedKV.v_head_dim, the key size unless given; none at all when a row is key and value at once, values_are_keys).
 """
 from __future__ import annotations
 
@@ -101,7 +101,8 @@ class CacheManager:
             for g, key in enumerate(self.group_keys):
                 shape = (len(self.group_entries[g]), self.num_pages[g] + 1, self.page_size)
                 self.k_arena.append(torch.zeros(shape + (key.width,), dtype=kv_dtype, device=device))
-                self.v_arena.append(torch.zeros(shape + (key.v_width,), dtype=kv_dtype, device=device))
+                # rows that are key and value at once have no arena of their own: the view's v is its k
+                self.v_arena.append(None if key.values_are_keys else torch.zeros(shape + (key.v_width,), dtype=kv_dtype, device=device))
             # every fixed-size state tensor is a stretch of ONE flat float32 arena, [slots, *shape] each, so that
             # the slots of requests that start in a step are zeroed by one kernel of the step's own chain
             # (state_segments: per tensor its offset in the arena and its floats per slot)
@@ -251,7 +252,8 @@ class CacheManager:
         for j, spec in enumerate(self._specs_of_entry.get(src, ())):
             if isinstance(spec, PagedKV):
                 g, idx = self._paged_of_entry[src]
-                out.append(PagedKVView(k=self.k_arena[g][idx], v=self.v_arena[g][idx], group=g, page_size=self.page_size,
+                k_view = self.k_arena[g][idx]
+                out.append(PagedKVView(k=k_view, v=k_view if self.v_arena[g] is None else self.v_arena[g][idx], group=g, page_size=self.page_size,
                                        n_pages=self.num_pages[g] + 1, window=spec.window, writes=owner is None))
             else:
                 if owner is not None:
@@ -263,5 +265,6 @@ class CacheManager:
     def bytes(self) -> int:
         n = 0
         for t in list(self.k_arena) + list(self.v_arena) + list(self.state.values()):
-            n += t.numel() * t.element_size()
+            if t is not None:
+                n += t.numel() * t.element_size()
         return n

@@ -10,17 +10,22 @@
 //      lane scores one key; running max and sum in 32-bit; then the lanes accumulate the values, each
 //      owning dimensions lane, lane+32, ...  The walk depends only on (position, window).
 //      With a sink the running max starts at 0 and the running sum at 1: the extra term is a key
-//      of score 0 seen before all others.  With a soft cap c the scaled score becomes c * tanh(score / c).
+//      of score 0 seen before all others; with sink values (one number per head) the extra term is exp(value) instead of 1:
+//      the running max starts at the head's value.  With a soft cap c the scaled score becomes c * tanh(score / c).
+//      Heads up to 512 wide (a cache of latent vectors that every head reads is one wide key/value head).
 //  (3) qkv_prepare_store: the same rows as a 32-bit product, for variants that work on whole heads in 32-bit before
 //      anything is rounded: biases added, half-split rotation, then q and k divided by their own root mean square
 //      per head (a norm without a weight), values optionally blended with the values another layer made for the
 //      same rows (v = (1 - lambda) v + lambda v_other, lambda a device scalar) and optionally saved for that use.
+//      v_from_k: the row has no value columns; a value head is the key head of the same number as it stands before the
+//      rotation (keys that are their own values).
 #include "common.cuh"
 
 namespace imparo {
 
 constexpr int ANY_MAX_HEAD = 256;
 constexpr int ANY_WARPS = 4;
+constexpr int ANY_ATT_MAX_HEAD = 512;          // attention_any alone takes heads this wide
 
 template <typename T>
 __global__ void __launch_bounds__(ANY_WARPS * 32)
@@ -162,7 +167,7 @@ qkv_prepare_store_kernel(const float* __restrict__ qkv, size_t in_width, const f
                          const T* __restrict__ v_other, const float* __restrict__ v_lambda, T* __restrict__ v_save,
                          T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                          const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                         int nh, int nkv, int hd, int vd, int* status) {
+                         int nh, int nkv, int hd, int vd, int v_from_k, int* status) {
     __shared__ float head[ANY_WARPS][ANY_MAX_HEAD];
     pdl_trigger();
     const int t = blockIdx.x;
@@ -174,7 +179,8 @@ qkv_prepare_store_kernel(const float* __restrict__ qkv, size_t in_width, const f
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
     const int kvh = is_q ? 0 : (is_k ? hh - nh : hh - nh - nkv);
     const int n = (is_q || is_k) ? hd : vd;
-    const size_t col = is_q ? (size_t)hh * hd : (size_t)nh * hd + (is_k ? (size_t)kvh * hd : (size_t)nkv * hd + (size_t)kvh * vd);
+    const size_t col = is_q ? (size_t)hh * hd
+                            : (size_t)nh * hd + ((is_k || v_from_k) ? (size_t)kvh * hd : (size_t)nkv * hd + (size_t)kvh * vd);
     T* dst = nullptr;
     int bad_page = 0;
     if (is_q) {
@@ -244,9 +250,9 @@ __global__ void __launch_bounds__(ANY_WARPS * 32)
 attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                      const int* __restrict__ positions, const int* __restrict__ item_of_token,
                      const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                     int window, float scale, int sink, float softcap, T* __restrict__ out, int nh, int nkv, int hd, int vd,
-                     int* status) {
-    __shared__ float qbuf[ANY_WARPS][ANY_MAX_HEAD];
+                     int window, float scale, int sink, const float* __restrict__ sink_values, float softcap,
+                     T* __restrict__ out, int nh, int nkv, int hd, int vd, int* status) {
+    __shared__ float qbuf[ANY_WARPS][ANY_ATT_MAX_HEAD];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -263,11 +269,11 @@ attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, con
     __syncwarp();
 
     const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-    constexpr int PER = ANY_MAX_HEAD / 32;
+    constexpr int PER = ANY_ATT_MAX_HEAD / 32;
     float acc[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    float m = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
 
     for (int base = lo; base <= pos; base += 32) {
         const int j = base + lane;
@@ -368,20 +374,20 @@ extern "C" int imparo_qkv_rotate_store(const void* qkv, int dtype, const int* po
 extern "C" int imparo_attention_any(const void* q, const void* k_cache, const void* v_cache, int dtype,
                                     const int* positions, const int* item_of_token,
                                     const int* table, int max_blocks, int page_size, int n_pages,
-                                    int window, float scale, int sink, float softcap, void* out,
+                                    int window, float scale, int sink, const float* sink_values, float softcap, void* out,
                                     int n_tok, int nh, int nkv, int hd, int vd, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
-    if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
+    if (hd < 1 || hd > ANY_ATT_MAX_HEAD || vd < 1 || vd > ANY_ATT_MAX_HEAD) return -3;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     dim3 grid(n_tok, (nh + ANY_WARPS - 1) / ANY_WARPS);
     if (dtype == IMPARO_DT_F32)
         launch(attention_any_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream,
                (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, item_of_token, table,
-               max_blocks, page_size, n_pages, window, scale, sink, softcap, (float*)out, nh, nkv, hd, vd, status);
+               max_blocks, page_size, n_pages, window, scale, sink, sink_values, softcap, (float*)out, nh, nkv, hd, vd, status);
     else if (dtype == IMPARO_DT_BF16)
         launch(attention_any_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream,
                (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions,
-               item_of_token, table, max_blocks, page_size, n_pages, window, scale, sink, softcap, (__nv_bfloat16*)out, nh, nkv, hd,
+               item_of_token, table, max_blocks, page_size, n_pages, window, scale, sink, sink_values, softcap, (__nv_bfloat16*)out, nh, nkv, hd,
                vd, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
@@ -394,22 +400,23 @@ extern "C" int imparo_qkv_prepare_store(const float* qkv, long long row_stride, 
                                         const int* item_of_token, const float* inv_freq, int n_rot, float unit_eps,
                                         const void* v_other, const float* v_lambda, void* v_save,
                                         void* q_out, void* k_cache, void* v_cache, const int* table, int max_blocks,
-                                        int page_size, int n_pages, int n_tok, int nh, int nkv, int hd, int vd, int* status,
-                                        cudaStream_t stream) {
+                                        int page_size, int n_pages, int n_tok, int nh, int nkv, int hd, int vd, int v_from_k,
+                                        int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
     if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
-    if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return -2;
+    if (v_from_k && vd != hd) return -6;
+    if (row_stride < (long long)(nh + nkv) * hd + (v_from_k ? 0 : (long long)nkv * vd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + ANY_WARPS - 1) / ANY_WARPS);
     if (dtype == IMPARO_DT_F32)
         launch(qkv_prepare_store_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream, qkv, (size_t)row_stride, bias, positions,
                item_of_token, inv_freq, n_rot, unit_eps, (const float*)v_other, v_lambda, (float*)v_save, (float*)q_out,
-               (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, status);
+               (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, v_from_k, status);
     else if (dtype == IMPARO_DT_BF16)
         launch(qkv_prepare_store_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream, qkv, (size_t)row_stride, bias, positions,
                item_of_token, inv_freq, n_rot, unit_eps, (const __nv_bfloat16*)v_other, v_lambda, (__nv_bfloat16*)v_save,
                (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv,
-               hd, vd, status);
+               hd, vd, v_from_k, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

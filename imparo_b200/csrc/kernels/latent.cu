@@ -1,0 +1,135 @@
+// Pieces of an attention whose keys and values are made from one small latent vector per token, which is all the
+// cache keeps.  With per-head matrices U_k [dim, rank] and U_v [vdim, rank] and the cached latent c_j,
+//   q . (U_k c_j) = (U_k^T q) . c_j      and      sum_j p_j (U_v c_j) = U_v (sum_j p_j c_j),
+// so the attention itself runs over the latents with every head sharing the one cached row per token: queries are
+// taken into the latent space before it and the result is taken out of it after it.
+//
+//  (1) latent_norm_store: per row of a 32-bit product [.. q latent .. | .. kv latent ..], each stretch divided by its
+//      root mean square times a weight; the query latent goes to an activation tensor, the kv latent into its page.
+//  (2) heads_linear: out[t, h, :] = W[h] x[t, h, :] for every head h (W [heads, out, in]), optionally times
+//      sigmoid(gate[t, h, :]) (a 32-bit product's columns).  A block takes a tile of rows of one head; the head's
+//      matrix is read once per tile.  32-bit sums, in order over `in`.
+#include "common.cuh"
+
+namespace imparo {
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_norm_store_kernel(const float* __restrict__ proj, size_t stride, int q_off, int q_rank, int c_off, int c_rank,
+                         const float* __restrict__ wq, const float* __restrict__ wc, float eps,
+                         const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                         T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ table, int max_blocks,
+                         int page_size, int n_pages, int* status) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const bool is_q = blockIdx.y == 0;
+    T* dst = nullptr;
+    int bad_page = 0;
+    if (is_q) {
+        dst = q_out + (size_t)t * q_rank;
+    } else {
+        const int pos = positions[t];
+        const int blk = pos / page_size;
+        int page = -1;
+        if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
+        if (page < 0 || page >= n_pages) bad_page = page;
+        else dst = cache + ((size_t)page * page_size + (pos % page_size)) * c_rank;
+    }
+    pdl_wait();
+    const int n = is_q ? q_rank : c_rank;
+    const float* src = proj + (size_t)t * stride + (is_q ? q_off : c_off);
+    const float* w = is_q ? wq : wc;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += src[i] * src[i];
+    ss = block_sum(ss, scratch);
+    if (dst == nullptr) {
+        if (threadIdx.x == 0) report(status, IMPARO_ST_PAGE_RANGE, 74, t, bad_page);
+        return;
+    }
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_f32<T>(src[i] * scale * w[i]);
+}
+
+constexpr int HL_ROWS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+heads_linear_kernel(const T* __restrict__ x, size_t x_stride, const T* __restrict__ w, const float* __restrict__ gate,
+                    size_t gate_stride, T* __restrict__ out, size_t out_stride, int n_tok, int n_in, int n_out) {
+    extern __shared__ float xs[];                       // [HL_ROWS, n_in]
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y;
+    const int t0 = blockIdx.x * HL_ROWS;
+    const int rows = min(HL_ROWS, n_tok - t0);
+    for (int e = threadIdx.x; e < HL_ROWS * n_in; e += blockDim.x) {
+        const int r = e / n_in, i = e % n_in;
+        xs[e] = r < rows ? to_f32(x[(size_t)(t0 + r) * x_stride + (size_t)h * n_in + i]) : 0.f;
+    }
+    __syncthreads();
+    const T* wh = w + (size_t)h * n_out * n_in;
+    for (int o = threadIdx.x; o < n_out; o += blockDim.x) {
+        float acc[HL_ROWS];
+#pragma unroll
+        for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
+        const T* wr = wh + (size_t)o * n_in;
+        for (int i = 0; i < n_in; ++i) {
+            const float wv = to_f32(wr[i]);
+#pragma unroll
+            for (int r = 0; r < HL_ROWS; ++r) acc[r] += wv * xs[r * n_in + i];
+        }
+#pragma unroll
+        for (int r = 0; r < HL_ROWS; ++r) {
+            if (r < rows) {
+                float v = acc[r];
+                if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)(t0 + r) * gate_stride + (size_t)h * n_out + o]));
+                out[(size_t)(t0 + r) * out_stride + (size_t)h * n_out + o] = from_f32<T>(v);
+            }
+        }
+    }
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+// proj: float32 rows of `stride` floats; q_out: [n_tok, q_rank] and cache pages of c_rank per position, both in dtype.
+extern "C" int imparo_latent_norm_store(const float* proj, long long stride, int q_off, int q_rank, int c_off, int c_rank,
+                                        const float* wq, const float* wc, float eps, const int* positions,
+                                        const int* item_of_token, void* q_out, void* cache, int dtype, const int* table,
+                                        int max_blocks, int page_size, int n_pages, int n_tok, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (q_rank < 1 || c_rank < 1 || stride < q_off + q_rank || stride < c_off + c_rank) return -2;
+    if (dtype == IMPARO_DT_F32)
+        launch(latent_norm_store_kernel<float>, dim3(n_tok, 2), dim3(128), 0, stream, proj, (size_t)stride, q_off, q_rank, c_off, c_rank,
+               wq, wc, eps, positions, item_of_token, (float*)q_out, (float*)cache, table, max_blocks, page_size, n_pages, status);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(latent_norm_store_kernel<__nv_bfloat16>, dim3(n_tok, 2), dim3(128), 0, stream, proj, (size_t)stride, q_off, q_rank, c_off,
+               c_rank, wq, wc, eps, positions, item_of_token, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, table, max_blocks,
+               page_size, n_pages, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// x: rows of x_stride elements holding heads * n_in; w: [heads, n_out, n_in]; gate: float32 rows (heads * n_out used) or null;
+// out: rows of out_stride elements holding heads * n_out.  x, w and out share the dtype.
+extern "C" int imparo_heads_linear(const void* x, long long x_stride, const void* w, const float* gate, long long gate_stride,
+                                   void* out, long long out_stride, int dtype, int n_tok, int heads, int n_in, int n_out,
+                                   cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (heads < 1 || n_in < 1 || n_out < 1) return -2;
+    const size_t smem = (size_t)HL_ROWS * n_in * sizeof(float);
+    if (smem > 48 * 1024) return -3;
+    const dim3 grid((n_tok + HL_ROWS - 1) / HL_ROWS, heads);
+    if (dtype == IMPARO_DT_F32)
+        launch(heads_linear_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, (size_t)x_stride, (const float*)w, gate,
+               (size_t)gate_stride, (float*)out, (size_t)out_stride, n_tok, n_in, n_out);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(heads_linear_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)x, (size_t)x_stride,
+               (const __nv_bfloat16*)w, gate, (size_t)gate_stride, (__nv_bfloat16*)out, (size_t)out_stride, n_tok, n_in, n_out);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

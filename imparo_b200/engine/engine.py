@@ -34,6 +34,20 @@ _PRECISIONS = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32",
 
 
 class Engine:
+    def _model_spec(self, folder: Optional[str]):
+        """The architecture's ModelSpec.  An architecture some of whose sizes only a tensor's shape gives takes the
+        folder's tensor shapes (name -> shape) as `tensor_shapes`."""
+        import inspect
+        import os
+        fn = self.arch.model_spec
+        path = os.path.join(folder, "model.safetensors") if folder is not None else None
+        if path is not None and os.path.isfile(path) and "tensor_shapes" in inspect.signature(fn).parameters:
+            from ..weights.safetensors_io import SafetensorsFile
+            with SafetensorsFile(path) as f:
+                shapes = {name: f.info(name)[1] for name in f.names()}
+            return fn(self.config, tensor_shapes=shapes)
+        return fn(self.config)
+
     def __init__(self, model: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
                  dtype: Optional[str] = None, device: Union[str, torch.device, None] = None, ctx: Optional[int] = None,
                  parallel: Optional[int] = None, page_size: Optional[int] = None, num_pages: Optional[int] = None,
@@ -78,7 +92,7 @@ class Engine:
         self.status = ops.new_status(self.device)
         self.rt = Runtime(precision=self.precision, device=self.device, status=self.status,
                           workspace=Workspace(self.device), launch_state=ops.LaunchState(cfg.switches))
-        self.model = Model(self.arch.model_spec(self.config), self.rt)
+        self.model = Model(self._model_spec(model), self.rt)
         specs = self.model.weight_specs()
         if model is not None:
             tensors = load_weights(model, specs, self.precision, self.device,

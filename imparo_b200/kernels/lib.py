@@ -116,8 +116,8 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])
     _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_act_rows_strided", [P, c_int64, P, I, I, I, I, S])
-    _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, c_float, P, I, I, I, I, I, P, S])
-    _declare(lib, "imparo_qkv_prepare_store", [P, c_int64, P, I, P, P, P, I, c_float, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, P, c_float, P, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_qkv_prepare_store", [P, c_int64, P, I, P, P, P, I, c_float, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_out_norm_add", [P, P, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_cast_rows", [P, P, I, c_int64, S])
     _declare(lib, "imparo_scale_rows", [P, c_int64, c_float, S])
@@ -131,6 +131,16 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, S])
     _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
+    _declare(lib, "imparo_streams_norm", [P, P, I, P, P, c_float, P, I, I, I, S])
+    _declare(lib, "imparo_streams_mix_add", [P, I, P, P, P, P, P, c_float, P, I, I, I, S])
+    _declare(lib, "imparo_embed_copies", [P, I, P, c_float, I, P, I, I, I, P, S])
+    _declare(lib, "imparo_channel_conv", [P, c_int64, I, I, I, P, P, P, P, P, P, I, I, P, c_int64, I, P, S])
+    _declare(lib, "imparo_channel_conv_state", [P, c_int64, I, I, I, P, P, P, P, I, I, S])
+    _declare(lib, "imparo_delta_prepare", [P, c_int64, I, I, P, c_int64, I, P, P, P, P, I, I, I, I, c_float, c_float, S])
+    _declare(lib, "imparo_delta_scan", [P, c_int64, I, I, I, P, P, P, P, P, I, I, P, I, I, I, I, P, S])
+    _declare(lib, "imparo_head_norm_gate", [P, P, c_float, P, c_int64, P, I, I, I, I, S])
+    _declare(lib, "imparo_latent_norm_store", [P, c_int64, I, I, I, I, P, P, c_float, P, P, P, P, I, P, I, I, I, I, P, S])
+    _declare(lib, "imparo_heads_linear", [P, c_int64, P, P, c_int64, P, c_int64, I, I, I, I, I, S])
     _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])
 
 

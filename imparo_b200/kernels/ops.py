@@ -77,6 +77,7 @@ class LaunchState:
         self.deferrable = set()      # data_ptr of streams whose next accumulate-product may stay pending
         self.pending = {}            # data_ptr -> (scratch, n_splits, rows, width)
         self.pending_mean = {}       # data_ptr -> arguments of a norm_mean_add the next reader of the stream carries out
+        self.pending_mix = {}        # data_ptr -> arguments of a streams_mix_add the next reader of the stream carries out
         self.partials = {}           # device index -> scratch of products into the stream
         self.consumer_parts = {}     # device index -> scratch of products a consumer kernel folds
         self.tc_scratch = {}         # device index -> (floats, counters) of the cluster-folded products
@@ -170,6 +171,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     _cuda(table, ids, out, status)
     _S.pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void
     _S.pending_mean.pop(out.data_ptr(), None)
+    _S.pending_mix.pop(out.data_ptr(), None)
     n, width = out.shape
     _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
     _need(out.dtype == torch.float32 and table.shape[1] == width, "embedding output is float32 [tokens, width]")
@@ -241,6 +243,9 @@ def settle(stream: torch.Tensor) -> None:
     pm = _S.pending_mean.pop(stream.data_ptr(), None)
     if pm is not None:
         norm_mean_add(stream, *pm)
+    px = _S.pending_mix.pop(stream.data_ptr(), None)
+    if px is not None:
+        streams_mix_add(stream, *px)
     p = _S.pending.pop(stream.data_ptr(), None)
     if p is not None:
         scratch, S, T, N = p
@@ -1090,11 +1095,13 @@ def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved
 
 
 def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale, sink,
-                  out, nh, nkv, hd, vd, status, softcap: float = 0.0) -> None:
-    """General attention: any head size hd and value size vd up to 256, optional window, optional sink (one more
-    term of score 0 and no value in the softmax's denominator), optional soft cap c > 0 on the scaled scores
-    (c * tanh(score / c)).  out [T, nh*vd]."""
-    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, status)
+                  out, nh, nkv, hd, vd, status, softcap: float = 0.0, sink_values: Optional[torch.Tensor] = None) -> None:
+    """General attention: any head size hd and value size vd up to 512, optional window, optional sink (one more
+    term in the softmax's denominator that has no value: of score 0, or with sink_values, float32 [nh], of the head's
+    own number, exp(value)), optional soft cap c > 0 on the scaled scores (c * tanh(score / c)).  out [T, nh*vd].
+    k_cache and v_cache may be the same tensor (keys that are their own values)."""
+    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, status, sink_values)
+    _need(sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == nh), "attention_any: sink values float32 [heads]")
     T = q.shape[0]
     _need(q.shape == (T, nh * hd) and out.shape == (T, nh * vd) and out.dtype == q.dtype, "attention_any: q/out shapes")
     _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
@@ -1103,21 +1110,23 @@ def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_siz
     _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
     _check(_lib.kernels().imparo_attention_any(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
-        table.shape[1], page_size, n_pages, int(window or 0), float(scale), int(bool(sink)), float(softcap or 0.0), _ptr(out),
-        T, nh, nkv, hd, vd, _ptr(status), _stream()), "attention_any")
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), int(bool(sink) or sink_values is not None),
+        _ptr(sink_values), float(softcap or 0.0), _ptr(out), T, nh, nkv, hd, vd, _ptr(status), _stream()), "attention_any")
 
 
 def qkv_prepare_store(qkv, bias, positions, item_of_token, inv_freq, n_rot, unit_eps, v_other, v_lambda, v_save, q_out,
-                      k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, vd, status) -> None:
+                      k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, vd, status, v_from_k: bool = False) -> None:
     """qkv: float32 [T, nh*hd + nkv*hd + nkv*vd] (a 32-bit product; rows dense, any row stride).  Per head, in 32-bit:
     + bias (float32 over the same columns, or None), half-split rotation of the first n_rot dimensions of q and k, then
     q and k divided by sqrt(mean(square) + unit_eps) (unit_eps None: kept as they are); q -> q_out [T, nh*hd], k and v
     into their pages.  v_other ([T, nkv*vd], the cache's dtype) with v_lambda (a float32 scalar on the device) blends
-    the values: v = (1 - lambda) v + lambda v_other; v_save ([T, nkv*vd]) receives the values before blending."""
+    the values: v = (1 - lambda) v + lambda v_other; v_save ([T, nkv*vd]) receives the values before blending.
+    v_from_k: qkv is [T, nh*hd + nkv*hd] and the values are the keys as they stand before the rotation (vd == hd)."""
     _need(qkv.is_cuda and qkv.stride(1) == 1 and qkv.dtype == torch.float32, "qkv_prepare_store: a float32 product with dense rows")
     _cuda(bias, positions, item_of_token, inv_freq, v_other, v_lambda, v_save, q_out, k_cache, v_cache, table, status)
     T = q_out.shape[0]
-    width = nh * hd + nkv * (hd + vd)
+    width = nh * hd + nkv * (hd + (0 if v_from_k else vd))
+    _need(not v_from_k or vd == hd, "qkv_prepare_store: keys as values need equal sizes")
     _need(tuple(qkv.shape) == (T, width) and q_out.shape[1] == nh * hd, "qkv_prepare_store: widths")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "qkv_prepare_store: bias float32 over the product's columns")
     _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
@@ -1135,8 +1144,8 @@ def qkv_prepare_store(qkv, bias, positions, item_of_token, inv_freq, n_rot, unit
     _check(_lib.kernels().imparo_qkv_prepare_store(
         _ptr(qkv), qkv.stride(0), _ptr(bias), _code(q_out), _ptr(positions), _ptr(item_of_token), _ptr(inv_freq), int(n_rot),
         -1.0 if unit_eps is None else float(unit_eps), _ptr(v_other), _ptr(v_lambda), _ptr(v_save), _ptr(q_out), _ptr(k_cache),
-        _ptr(v_cache), _ptr(table), table.shape[1], page_size, n_pages, T, nh, nkv, hd, vd, _ptr(status), _stream()),
-        "qkv_prepare_store")
+        _ptr(v_cache), _ptr(table), table.shape[1], page_size, n_pages, T, nh, nkv, hd, vd, int(bool(v_from_k)), _ptr(status),
+        _stream()), "qkv_prepare_store")
 
 
 # ---- linear attention with decay (csrc/kernels/linear_attention.cu) -------------------------------------------
@@ -1376,3 +1385,191 @@ def moe_experts(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: 
     _check(_lib.kernels().imparo_moe_rows(_ptr(h), _ptr(w_gu), _ptr(w_down), _code(h), _ptr(ids), _ptr(wts), n, width, ff, int(top), E,
                                           int(bool(weight_input)), _ptr(mid), _ptr(out), _stream()), "moe_rows")
     COUNTS["own"] += 1
+
+
+# ---- a stream kept as n copies per token (csrc/kernels/hyper_connections.cu) -----------------------------------
+def embed_copies(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor, scale: float = 1.0,
+                 copies: int = 1) -> None:
+    """out [T, copies * width] float32: the embedding row times scale, written into every copy."""
+    _cuda(table, ids, out, status)
+    for d in (_S.pending, _S.pending_mean, _S.pending_mix):      # the stream starts afresh
+        d.pop(out.data_ptr(), None)
+    n = out.shape[0]
+    width = table.shape[1]
+    _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
+    _need(out.dtype == torch.float32 and out.shape[1] == copies * width and out.is_contiguous(),
+          "embedding output is float32 [tokens, copies * width]")
+    _check(_lib.kernels().imparo_embed_copies(_ptr(table), _code(table), _ptr(ids), float(scale), int(copies), _ptr(out), n, width,
+                                              table.shape[0], _ptr(status), _stream()), "embed_copies")
+
+
+def streams_norm(x: torch.Tensor, n: int, coef: Optional[torch.Tensor], w: torch.Tensor, eps: float, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = u / rms(u) * w with u = sum_s coef[s] x[row, s] (coef None: the plain sum of the n copies).
+    x: float32 [*, n * width]; rows (int32) picks input rows.  A streams_mix_add left pending on x is carried out
+    by the same kernel when the norm reads every row in place."""
+    _cuda(x, coef, w, out, rows)
+    n_rows, width = out.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == n * width, "streams_norm: x float32 [rows, n * width]")
+    _need(w.dtype == torch.float32 and w.numel() == width, "streams_norm: weight float32 [width]")
+    _need(coef is None or (coef.dtype == torch.float32 and coef.numel() == n), "streams_norm: coefficients float32 [n]")
+    px = _S.pending_mix.get(x.data_ptr())
+    if px is not None and rows is None and x.shape[0] == n_rows and px[0] == n and x.data_ptr() not in _S.pending:
+        _S.pending_mix.pop(x.data_ptr())
+        _, mix, b, y = px
+        _check(_lib.kernels().imparo_streams_mix_add(_ptr(x), n, _ptr(mix), _ptr(b), _ptr(y), _ptr(coef), _ptr(w), float(eps),
+                                                     _ptr(out), _code(out), n_rows, width, _stream()), "streams_mix_add_norm")
+        return
+    settle(x)
+    if rows is None:
+        _need(x.shape[0] >= n_rows, "streams_norm: fewer input rows than output rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "streams_norm: rows must be int32, one per output row")
+    _check(_lib.kernels().imparo_streams_norm(_ptr(x), _ptr(rows), n, _ptr(coef), _ptr(w), float(eps), _ptr(out), _code(out),
+                                              n_rows, width, _stream()), "streams_norm")
+
+
+def streams_mix_add(x: torch.Tensor, n: int, mix: torch.Tensor, b: torch.Tensor, y: torch.Tensor, defer: bool = False) -> None:
+    """x'[r, t] = sum_s mix[s, t] x[r, s] + b[t] y[r] for all n copies at once.  x: float32 [rows, n * width] in place;
+    mix float32 [n, n] ([from, to]); b float32 [n]; y float32 [rows, width].  defer: the update is left to the next
+    reader of x (streams_norm does it in its own pass; settle() does it alone); y must stay as it is until then."""
+    _cuda(x, mix, b, y)
+    rows, width = y.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (rows, n * width), "streams_mix_add: x float32 [rows, n * width]")
+    _need(y.dtype == torch.float32 and y.is_contiguous(), "streams_mix_add: y float32 [rows, width]")
+    _need(mix.dtype == torch.float32 and mix.numel() == n * n and b.dtype == torch.float32 and b.numel() == n,
+          "streams_mix_add: mix float32 [n, n], b float32 [n]")
+    settle(x)
+    settle(y)
+    if defer:
+        _S.pending_mix[x.data_ptr()] = (n, mix, b, y)
+        return
+    _check(_lib.kernels().imparo_streams_mix_add(_ptr(x), n, _ptr(mix), _ptr(b), _ptr(y), None, None, 0.0, None, 0, rows, width,
+                                                 _stream()), "streams_mix_add")
+
+
+# ---- short convolution over time on the channels of a 32-bit product (csrc/kernels/channel_conv.cu) --------------
+def channel_conv(proj: torch.Tensor, col0: int, channels: int, taps: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+                 state: torch.Tensor, item_row_start, item_of_token, item_slot, n_items: int, out: torch.Tensor,
+                 status: torch.Tensor, act: Optional[str] = None) -> None:
+    """out[t, c] = act(sum_j w[c, j] * u[t - taps + 1 + j, c]), u = proj[:, col0 + c] (+ bias[c]); inputs before a portion's
+    first row come from the request's slot of state (float32 [slots, taps - 1, channels], the last inputs, oldest first),
+    which is then moved on by the portion's rows.  proj, out: float32, rows dense.  act: None | "silu"."""
+    _cuda(w, bias, state, item_row_start, item_of_token, item_slot, status)
+    _need(proj.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = out.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[0] == T and proj.shape[1] >= col0 + channels,
+          "channel_conv: a float32 product with dense rows")
+    _need(out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == channels, "channel_conv: out float32 [T, channels]")
+    _need(w.dtype == torch.float32 and tuple(w.shape) == (channels, taps) and w.is_contiguous(), "channel_conv: taps float32 [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == channels), "channel_conv: bias float32 [channels]")
+    _need(act in (None, "silu"), "channel_conv: act is None or 'silu'")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 3 and state.shape[2] == channels
+          and state.shape[1] >= max(taps - 1, 1), "channel_conv: state float32 [slots, taps - 1, channels]")
+    _need(state.shape[1] == taps - 1 or taps == 1, "channel_conv: state holds taps - 1 rows")
+    _check(_lib.kernels().imparo_channel_conv(_ptr(proj), proj.stride(0), int(col0), channels, taps, _ptr(w), _ptr(bias), _ptr(state),
+                                              _ptr(item_row_start), _ptr(item_of_token), _ptr(item_slot), state.shape[0],
+                                              1 if act == "silu" else 0, _ptr(out), out.stride(0), T, _ptr(status), _stream()),
+           "channel_conv")
+    if taps > 1:
+        _check(_lib.kernels().imparo_channel_conv_state(_ptr(proj), proj.stride(0), int(col0), channels, taps, _ptr(bias), _ptr(state),
+                                                        _ptr(item_row_start), _ptr(item_slot), state.shape[0], n_items, _stream()),
+               "channel_conv_state")
+
+
+# ---- gated delta rule with a decay per key channel (csrc/kernels/delta_rule.cu) ----------------------------------
+def delta_prepare(qkv: torch.Tensor, q_off: int, k_off: int, bproj: torch.Tensor, b_off: int, a: torch.Tensor, A_log: torch.Tensor,
+                  dt_bias: torch.Tensor, beta: torch.Tensor, heads: int, kv_heads: int, dim: int, unit_eps: float,
+                  q_scale: float) -> None:
+    """In 32-bit, per row: the kv_heads query heads (at q_off) and key heads (at k_off) of qkv divided by
+    sqrt(sum of squares + unit_eps), queries also times q_scale; beta[t, h] = sigmoid(bproj[t, b_off + h]);
+    a [T, heads * dim] becomes exp(-exp(A_log[h]) * softplus(a + dt_bias))."""
+    _cuda(a, A_log, dt_bias, beta)
+    _need(qkv.is_cuda and bproj.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = qkv.shape[0]
+    for t in (qkv, bproj, a, A_log, dt_bias, beta):
+        _need(t.dtype == torch.float32, "delta_prepare: float32 tensors")
+    _need(qkv.stride(1) == 1 and bproj.stride(1) == 1 and a.is_contiguous() and beta.is_contiguous(), "delta_prepare: dense rows")
+    _need(tuple(a.shape) == (T, heads * dim) and tuple(beta.shape) == (T, heads) and A_log.numel() == heads
+          and dt_bias.numel() == heads * dim, "delta_prepare: shapes")
+    _need(qkv.shape[1] >= max(q_off, k_off) + kv_heads * dim and bproj.shape[1] >= b_off + heads and bproj.shape[0] == T,
+          "delta_prepare: column ranges")
+    _check(_lib.kernels().imparo_delta_prepare(_ptr(qkv), qkv.stride(0), int(q_off), int(k_off), _ptr(bproj), bproj.stride(0), int(b_off),
+                                               _ptr(a), _ptr(A_log), _ptr(dt_bias), _ptr(beta), T, heads, kv_heads, dim, float(unit_eps),
+                                               float(q_scale), _stream()), "delta_prepare")
+
+
+def delta_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               item_row_start, item_slot, n_items: int, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+               status: torch.Tensor) -> None:
+    """Per request and value head, rows in order: S = g * S; u = beta (v - S^T k); S += k u^T; out = S^T q.
+    qkv float32 rows (query / key heads kv_heads * dim at q_off / k_off, values heads * vdim at v_off); g float32
+    [T, heads * dim]; beta float32 [T, heads]; state float32 [slots, heads, dim, vdim]; out float32 [T, heads * vdim]."""
+    _cuda(g, beta, state, item_row_start, item_slot, out, status)
+    _need(qkv.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = qkv.shape[0]
+    for t in (qkv, g, beta, state, out):
+        _need(t.dtype == torch.float32, "delta_scan: float32 tensors")
+    _need(qkv.stride(1) == 1 and g.is_contiguous() and beta.is_contiguous() and out.is_contiguous() and state.is_contiguous(),
+          "delta_scan: dense rows")
+    _need(tuple(g.shape) == (T, heads * dim) and tuple(beta.shape) == (T, heads) and tuple(out.shape) == (T, heads * vdim),
+          "delta_scan: shapes")
+    _need(tuple(state.shape[1:]) == (heads, dim, vdim), "delta_scan: state [slots, heads, dim, vdim]")
+    _need(1 <= dim <= 256, "delta_scan: key size 1 to 256")
+    _need(qkv.shape[1] >= max(q_off + kv_heads * dim, k_off + kv_heads * dim, v_off + heads * vdim), "delta_scan: column ranges")
+    _check(_lib.kernels().imparo_delta_scan(_ptr(qkv), qkv.stride(0), int(q_off), int(k_off), int(v_off), _ptr(g), _ptr(beta), _ptr(state),
+                                            _ptr(item_row_start), _ptr(item_slot), state.shape[0], n_items, _ptr(out), heads, kv_heads,
+                                            dim, vdim, _ptr(status), _stream()), "delta_scan")
+
+
+def head_norm_gate(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int, vdim: int) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * w * sigmoid(gate[t, h]) per head.  o float32 [T, heads * vdim]; w float32 [vdim];
+    gate float32 rows (dense, any row stride)."""
+    _cuda(o, w, out)
+    _need(gate.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and tuple(o.shape) == (T, heads * vdim), "head_norm_gate: o float32 [T, heads * vdim]")
+    _need(w.dtype == torch.float32 and w.numel() == vdim, "head_norm_gate: weight float32 [vdim]")
+    _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (T, heads * vdim), "head_norm_gate: gate float32")
+    _need(out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "head_norm_gate: out [T, heads * vdim]")
+    _check(_lib.kernels().imparo_head_norm_gate(_ptr(o), _ptr(w), float(eps), _ptr(gate), gate.stride(0), _ptr(out), _code(out), T,
+                                                heads, vdim, _stream()), "head_norm_gate")
+
+
+# ---- attention over cached latent vectors (csrc/kernels/latent.cu) ----------------------------------------------
+def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, c_rank: int, wq: torch.Tensor, wc: torch.Tensor,
+                      eps: float, positions, item_of_token, q_out: torch.Tensor, cache: torch.Tensor, table, page_size: int,
+                      n_pages: int, status: torch.Tensor) -> None:
+    """Two stretches of a 32-bit product row, each divided by its root mean square times a weight: the query latent
+    -> q_out [T, q_rank], the key/value latent -> the row's place in the paged cache (rows of c_rank)."""
+    _cuda(wq, wc, positions, item_of_token, q_out, cache, table, status)
+    _need(proj.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = q_out.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[0] == T, "latent_norm_store: a float32 product with dense rows")
+    _need(proj.shape[1] >= max(q_off + q_rank, c_off + c_rank), "latent_norm_store: column ranges")
+    _need(wq.dtype == torch.float32 and wq.numel() == q_rank and wc.dtype == torch.float32 and wc.numel() == c_rank,
+          "latent_norm_store: weights float32")
+    _need(q_out.is_contiguous() and q_out.shape[1] == q_rank and cache.dtype == q_out.dtype, "latent_norm_store: q_out / cache dtype")
+    _need(cache.numel() >= n_pages * page_size * c_rank, "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _check(_lib.kernels().imparo_latent_norm_store(_ptr(proj), proj.stride(0), int(q_off), q_rank, int(c_off), c_rank, _ptr(wq), _ptr(wc),
+                                                   float(eps), _ptr(positions), _ptr(item_of_token), _ptr(q_out), _ptr(cache),
+                                                   _code(q_out), _ptr(table), table.shape[1], page_size, n_pages, T, _ptr(status),
+                                                   _stream()), "latent_norm_store")
+
+
+def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :] = w[h] x[t, h, :] for every head (w [heads, n_out, n_in]; x [T, heads * n_in], out [T, heads * n_out],
+    rows dense), optionally times sigmoid(gate[t, h, :]) (float32 [T, heads * n_out], rows dense).  32-bit sums."""
+    _cuda(w)
+    _need(x.is_cuda and out.is_cuda and (gate is None or gate.is_cuda), "kernels run on CUDA tensors only (there is no CPU path)")
+    heads, n_out, n_in = w.shape
+    T = x.shape[0]
+    _need(x.dtype == w.dtype == out.dtype and w.is_contiguous(), "heads_linear: one dtype, dense weights")
+    _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(x.shape) == (T, heads * n_in) and tuple(out.shape) == (T, heads * n_out),
+          "heads_linear: shapes")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (T, heads * n_out)),
+          "heads_linear: gate float32 [T, heads * n_out]")
+    _need(n_in * 32 <= 48 * 1024, "heads_linear: input size per head up to 1536")
+    _check(_lib.kernels().imparo_heads_linear(_ptr(x), x.stride(0), _ptr(w), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                              _ptr(out), out.stride(0), _code(x), T, heads, n_in, n_out, _stream()), "heads_linear")

@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import ops
 from .base import Part, make_part
-from .spec import PagedKV, PartSpec, WeightSpec
+from .spec import PagedKV, PartSpec, SlotState, WeightSpec
 
 
 class AttentionMixer(Part):
@@ -28,7 +28,10 @@ class AttentionMixer(Part):
     square per head, eps as given, no weight), bias "required" (q/k/v biases that the file must carry, added in 32-bit
     before the rotation), v_share ({"role": "source" | "blend", "lambda": tensor name}: the source layer leaves the values
     it made for the step's rows to later layers of the same step; a blending layer stores (1 - lambda) v + lambda v_source,
-    lambda its own scalar tensor).
+    lambda its own scalar tensor), qk_conv ({"taps": n, "q": tensor name, "k": tensor name}: a causal convolution over time on
+    every channel of q and of k, taps [channels, n] with the last column on the current token, right after the projection
+    and its bias; the last n - 1 projected rows of a request live in its state slot), v_from_k (bool: there is no value
+    projection; a key head as it stands before the rotation is also the value head, so the value size is the head size).
 
     Shapes and variants the specialised kernels do not take (a value size of its own, a sink, a rotation of interleaved
     pairs or with a magnitude, a head size that is no multiple of 16) run on the general pair of kernels
@@ -72,8 +75,15 @@ class AttentionMixer(Part):
         if self.v_share is not None and self.v_share.get("role") not in ("source", "blend"):
             raise ValueError("attention: v_share role must be 'source' or 'blend'")
         self.bias_required = p.get("bias") == "required"
-        # whole heads in 32-bit before anything is rounded: biases, rotation, the norm without a weight, shared values
-        self.prepared = self.unit_norm or self.v_share is not None or self.bias_required
+        self.qk_conv = dict(p["qk_conv"]) if p.get("qk_conv") else None
+        self.v_from_k = bool(p.get("v_from_k", False))
+        if self.v_from_k and (self.vd != self.hd or self.v_share is not None):
+            raise ValueError("attention: keys that are their own values need value size = head size and no shared values")
+        if self.qk_conv is not None and not 1 <= int(self.qk_conv["taps"]) <= 17:
+            raise ValueError(f"attention: {self.qk_conv['taps']} conv taps are not supported by the kernel (1 to 17)")
+        # whole heads in 32-bit before anything is rounded: biases, convolution, rotation, the norm without a weight, shared values
+        self.prepared = (self.unit_norm or self.v_share is not None or self.bias_required or self.qk_conv is not None
+                         or self.v_from_k)
         self.general = (self.sink or self.vd != self.hd or self.hd % 16 != 0 or self.position.interleaved
                         or self.position.magnitude != 1.0 or self.prepared or self.softcap > 0.0)
         if self.prepared and (self.qk_norm or self.position.interleaved or self.position.magnitude != 1.0):
@@ -89,13 +99,20 @@ class AttentionMixer(Part):
         n, H, hd, vd = self.names, self.hidden, self.hd, self.vd
         specs = [WeightSpec(n["q"], ((self.nh * hd, H),)), WeightSpec(n["k"], ((self.nkv * hd, H),)),
                  WeightSpec(n["v"], ((self.nkv * vd, H),)), WeightSpec(n["o"], ((H, self.nh * vd),))]
+        if self.v_from_k:
+            del specs[2]
+        if self.qk_conv is not None:
+            taps = int(self.qk_conv["taps"])
+            specs += [WeightSpec(self.prefix + self.qk_conv["q"], ((self.nh * hd, taps),), role="vector", init=("conv_taps",)),
+                      WeightSpec(self.prefix + self.qk_conv["k"], ((self.nkv * hd, taps),), role="vector", init=("conv_taps",))]
         if self.qk_norm:
             specs += [WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
                       WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))]
         if self.bias_required:
             specs += [WeightSpec(n["q_bias"], ((self.nh * hd,),), role="vector", init=("bias",)),
-                      WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",)),
-                      WeightSpec(n["v_bias"], ((self.nkv * vd,),), role="vector", init=("bias",))]
+                      WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",))]
+            if not self.v_from_k:
+                specs.append(WeightSpec(n["v_bias"], ((self.nkv * vd,),), role="vector", init=("bias",)))
         elif self.bias:
             specs += [WeightSpec(n["q_bias"], ((self.nh * hd,),), role="vector", init=("bias",), optional=True),
                       WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",), optional=True),
@@ -108,15 +125,18 @@ class AttentionMixer(Part):
     def bind(self, tensors):
         n = self.names
         # one fused projection [q | k | v]: a layout choice, the arithmetic is unchanged
-        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]]] + ([] if self.v_from_k else [tensors[n["v"]]]), dim=0).contiguous()
+        if self.qk_conv is not None:
+            self.conv_w = torch.cat([tensors[self.prefix + self.qk_conv["q"]], tensors[self.prefix + self.qk_conv["k"]]], dim=0).contiguous()
         self.w_o = tensors[n["o"]]
         self.q_norm = tensors[n["q_norm"]] if self.qk_norm else None
         self.k_norm = tensors[n["k_norm"]] if self.qk_norm else None
         if self.v_share is not None:
             self.v_lambda = tensors[self.prefix + self.v_share["lambda"]].reshape(1).float().contiguous()
         if self.bias:
-            parts = [(tensors.get(n["q_bias"]), self.nh * self.hd), (tensors.get(n["k_bias"]), self.nkv * self.hd),
-                     (tensors.get(n["v_bias"]), self.nkv * self.vd)]
+            parts = [(tensors.get(n["q_bias"]), self.nh * self.hd), (tensors.get(n["k_bias"]), self.nkv * self.hd)]
+            if not self.v_from_k:
+                parts.append((tensors.get(n["v_bias"]), self.nkv * self.vd))
             if any(t is not None for t, _ in parts):      # one vector [q | k | v], zeros where the file has none
                 ref = self.w_o
                 self.b_qkv = torch.cat([t.float() if t is not None else torch.zeros(w, dtype=torch.float32, device=ref.device)
@@ -125,7 +145,10 @@ class AttentionMixer(Part):
         self.position.bind(tensors)
 
     def cache_specs(self):
-        return (PagedKV(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd),)
+        paged = PagedKV(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd)
+        if self.qk_conv is not None:
+            return (paged, SlotState((max(int(self.qk_conv["taps"]) - 1, 1), (self.nh + self.nkv) * self.hd)))
+        return (paged,)
 
     def _partials_room(self, upper_context: int) -> int:
         """Partial results (per head) that the split-key attention of this engine's largest step of one-token rows
@@ -148,12 +171,12 @@ class AttentionMixer(Part):
     def adopt_input_weight(self, view) -> None:
         self.w_qkv = view
 
-    def _forward_general(self, x, batch, kv, residual, accumulate, projected=None):
+    def _forward_general(self, x, batch, kv, residual, accumulate, projected=None, conv_state=None):
         """Product (unless the arrangement made it), rotation + cache write, attention, output product."""
         rt, T = self.rt, x.shape[0]
         nh, hd, vd = self.nh, self.hd, self.vd
         nkv = self.nkv if kv.writes else 0
-        width = nh * hd + nkv * (hd + vd)
+        width = nh * hd + nkv * (hd + (0 if self.v_from_k else vd))
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype, first="tokens")
         rot = self.position.rotary()
         inv_freq, n_rot = rot if rot is not None else (None, 0)
@@ -164,6 +187,13 @@ class AttentionMixer(Part):
             # the product in 32-bit, so that biases, angles and the norm without a weight see unrounded heads
             qkv = rt.workspace.get("attn_qkv32", (T, width), torch.float32, first="tokens")
             ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+            bias = self.b_qkv
+            if self.qk_conv is not None:
+                # the convolution reads the biased product (the bias is the projection's) and leaves plain 32-bit rows
+                conv = rt.workspace.get("attn_qk_conv32", (T, width), torch.float32, first="tokens")
+                ops.channel_conv(qkv, 0, width, int(self.qk_conv["taps"]), self.conv_w, bias, conv_state.state, batch.item_row_start,
+                                 batch.item_of_token, batch.item_slot, batch.n_items, conv, rt.status)
+                qkv, bias = conv, None
             v_other = v_save = None
             if self.v_share is not None:
                 notes = batch.notes
@@ -174,9 +204,10 @@ class AttentionMixer(Part):
                     v_other = notes.get(key)
                     if v_other is None:
                         raise ValueError("attention: a layer blends shared values, but no earlier layer of the step left any")
-            ops.qkv_prepare_store(qkv, self.b_qkv, batch.positions, batch.item_of_token, inv_freq, n_rot,
+            ops.qkv_prepare_store(qkv, bias, batch.positions, batch.item_of_token, inv_freq, n_rot,
                                   self.eps if self.unit_norm else None, v_other, self.v_lambda if v_other is not None else None,
-                                  v_save, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
+                                  v_save, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status,
+                                  v_from_k=self.v_from_k)
         else:
             if projected is not None and kv.writes:
                 qkv = projected
@@ -221,7 +252,8 @@ class AttentionMixer(Part):
     def forward(self, x, batch, caches, residual, accumulate=True, projected=None):
         kv = caches[0]
         if self.general:
-            return self._forward_general(x, batch, kv, residual, accumulate, projected)
+            return self._forward_general(x, batch, kv, residual, accumulate, projected,
+                                         conv_state=caches[1] if self.qk_conv is not None else None)
         if not accumulate:
             residual.zero_()              # the specialised path's products add; the caller's buffer starts from nothing
         rt, T = self.rt, x.shape[0]

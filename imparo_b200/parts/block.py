@@ -290,3 +290,93 @@ class OutputNormResidualBlock(Block):
         if probe:
             probe("stream_out", x)
         return None
+
+
+class HyperConnectionBlock(Block):
+    """The stream is kept as n copies per token, x [tokens, n * width] ("hyper-connections").  For each sublayer f (the
+    mixer, then the feed-forward if the layer has one) with its own tensors a [n], b [n], M [n, n] (indexed [from, to]):
+
+        u = sum_s a[s] x_s;   y = f(norm(u));   x_t <- sum_s M[s, t] x_s + b[t] y      (all copies at once from the old ones)
+
+    params: layer (LayerSpec): mixer_norm / feed_forward_norm are "rmsnorm" parts with `streams` = n and `stream_weights` =
+    the name of a; layer.params: "streams" (n), "mixer_hc" and "feed_forward_hc" ({"out": name of b, "mix": name of M}).
+    Sublayers write their output into a float32 buffer (forward(..., accumulate=False)).  The update of the copies is left
+    to the next reader of the stream: the next sublayer's norm (of this block or of the one after it) mixes, adds and norms
+    in one pass.  As the model's last block the feed-forward runs on the wanted rows only.  n = 1 with a = b = M = 1 is the
+    plain pre-norm block."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        spec = params["layer"]
+        self.n = int(spec.params["streams"])
+        self.mixer_norm = make_part("norm", spec.mixer_norm, prefix, rt)
+        self.mixer = make_part("mixer", spec.mixer, prefix, rt)
+        self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt) if spec.feed_forward is not None else None
+        self.ff_norm = make_part("norm", spec.feed_forward_norm, prefix, rt) if self.ff is not None else None
+        self.hc_names = [dict(spec.params["mixer_hc"])] + ([dict(spec.params["feed_forward_hc"])] if self.ff is not None else [])
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff) if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.picks_rows = True
+        self.hc = []
+
+    def weight_specs(self):
+        from .spec import WeightSpec
+        n = self.n
+        specs = [w for p in self.parts for w in p.weight_specs()]
+        for names in self.hc_names:
+            specs += [WeightSpec(self.prefix + names["out"], ((n,),), role="vector", init=("uniform", 0.5, 1.0)),
+                      WeightSpec(self.prefix + names["mix"], ((n, n),), role="vector", init=("uniform", 0.0, 0.6))]
+        return specs
+
+    def bind(self, tensors):
+        for p in self.parts:
+            p.bind(tensors)
+        self.hc = [(tensors[self.prefix + names["mix"]].contiguous(), tensors[self.prefix + names["out"]]) for names in self.hc_names]
+
+    def cache_specs(self):
+        return self.mixer.cache_specs()
+
+    def forward(self, x, batch, caches, only_rows=None):
+        import torch
+        from ..kernels import ops
+        probe = self.rt.probe if self.rt.probe_now else None
+        ws = self.rt.workspace
+        width = x.shape[1] // self.n
+        if probe:
+            ops.settle(x)
+            probe("stream_in", x)
+        h = self.mixer_norm.forward(x, tag="normed_mixer")           # (carries out the update the sublayer before left pending)
+        if probe:
+            probe("mixer_norm", h)
+        y = ws.get("sublayer_out", (x.shape[0], width), torch.float32, first="tokens")
+        self.mixer.forward(h, batch, caches, y, accumulate=False)
+        mix, out = self.hc[0]
+        ops.streams_mix_add(x, self.n, mix, out, y, defer=not probe)
+        if probe:
+            probe("stream_mixer", x)
+        if only_rows is not None:
+            rows, n = only_rows
+            if n == 0:
+                ops.settle(x)
+                return None
+            xs = ws.get("stream_picked", (n, x.shape[1]), x.dtype, first="rows")
+            ops.gather_rows(x, rows, xs)
+            if self.ff is not None:
+                hs = self.ff_norm.forward(xs, tag="normed_ff_picked")
+                ys = ws.get("sublayer_out_picked", (n, width), torch.float32, first="rows")
+                self.ff.forward(hs, batch, ys, accumulate=False)
+                mix, out = self.hc[1]
+                ops.streams_mix_add(xs, self.n, mix, out, ys)
+            if probe:
+                probe("stream_out", xs)
+            return xs
+        if self.ff is not None:
+            h = self.ff_norm.forward(x, tag="normed_ff")
+            if probe:
+                probe("ff_norm", h)
+            self.ff.forward(h, batch, y, accumulate=False)
+            mix, out = self.hc[1]
+            ops.streams_mix_add(x, self.n, mix, out, y, defer=not probe)
+        if probe:
+            probe("stream_out", x)
+        return None

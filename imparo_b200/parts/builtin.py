@@ -1,9 +1,11 @@
 """Registers the built-in parts."""
 from .attention import AttentionMixer
 from .base import register_part
-from .block import OutputNormResidualBlock, ParallelResidualBlock, PreNormResidualBlock
+from .block import HyperConnectionBlock, OutputNormResidualBlock, ParallelResidualBlock, PreNormResidualBlock
+from .delta_rule import GatedDeltaRule
 from .embedding import LinearHead, TokenEmbedding
 from .feedforward import DenseFeedForward, SwiGLU
+from .latent_attention import LatentAttention
 from .linear_attention import DecayLinearAttention
 from .mamba2 import Mamba2Mixer
 from .moe import RoutedExperts
@@ -31,3 +33,6 @@ register_part("stream_op", "stretch_entry", StretchEntry, replace=True)
 register_part("block", "outnorm_residual", OutputNormResidualBlock, replace=True)
 register_part("mixer", "mamba2", Mamba2Mixer, replace=True)
 register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
+register_part("block", "hyper_connections", HyperConnectionBlock, replace=True)
+register_part("mixer", "latent_attention", LatentAttention, replace=True)
+register_part("mixer", "gated_delta_rule", GatedDeltaRule, replace=True)

@@ -14,13 +14,16 @@ from .spec import WeightSpec
 
 
 class TokenEmbedding(Part):
-    """params: vocab, width, name."""
+    """params: vocab, width, name, scale (optional factor on the rows, applied in 32-bit), copies (optional n > 1: the
+    stream holds n copies of every row side by side, [tokens, n * width], for arrangements that keep several)."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.vocab = int(params["vocab"])
         self.width = int(params["width"])
         self.name = prefix + params["name"]
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
+        self.copies = int(params.get("copies") or 1)
         self.table = None
 
     def weight_specs(self):
@@ -32,8 +35,11 @@ class TokenEmbedding(Part):
     def forward(self, batch) -> torch.Tensor:
         """batch: the step's batch (token_ids, positions, item_of_token, ... on the device).  This part reads
         the token ids only; an embedding that adds learned positions or segment rows reads the rest."""
-        out = self.rt.workspace.get("residual", (batch.n_tokens, self.width), torch.float32, first="tokens")
-        ops.embed_gather(self.table, batch.token_ids, out, self.rt.status)
+        out = self.rt.workspace.get("residual", (batch.n_tokens, self.copies * self.width), torch.float32, first="tokens")
+        if self.scale != 1.0 or self.copies != 1:
+            ops.embed_copies(self.table, batch.token_ids, out, self.rt.status, scale=self.scale, copies=self.copies)
+        else:
+            ops.embed_gather(self.table, batch.token_ids, out, self.rt.status)
         return out
 
 

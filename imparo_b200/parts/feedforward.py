@@ -11,7 +11,8 @@ from .spec import WeightSpec
 
 
 class SwiGLU(Part):
-    """params: hidden, ff, names (optional)."""
+    """params: hidden, ff, names (optional).  forward(..., accumulate=False) overwrites `residual` (then any float32
+    [tokens, hidden] buffer) instead of adding into it."""
     adds_with_linear = True
 
 
@@ -34,12 +35,12 @@ class SwiGLU(Part):
         self.w_gu = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
         self.w_down = tensors[n["down"]]
 
-    def forward(self, x, batch, residual):
+    def forward(self, x, batch, residual, accumulate=True):
         rt, T, F = self.rt, x.shape[0], self.ff
         h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype, first="tokens")
         # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
         ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
-        ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)
+        ops.linear(h, self.w_down, residual, accumulate=accumulate, status=rt.status)
 
 
 class DenseFeedForward(Part):

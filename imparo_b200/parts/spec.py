@@ -90,6 +90,7 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None        # None: values are as wide as keys
+    values_are_keys: bool = False           # True: one row per position serves as key and as value (no value arena)
 
     @property
     def width(self) -> int:
@@ -97,6 +98,8 @@ class PagedKV:
 
     @property
     def v_width(self) -> int:
+        if self.values_are_keys:
+            return 0
         return self.n_kv_heads * (self.head_dim if self.v_head_dim is None else self.v_head_dim)
 
 
