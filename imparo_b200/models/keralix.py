@@ -66,14 +66,11 @@ def keralix_model_spec(cfg: KeralixConfig, tensor_shapes=None) -> ModelSpec:
         if L.mlp is not None:
             ff = PartSpec("swiglu", {"hidden": W, "ff": L.mlp.ff, "names": {"gate": "mlp.gate", "up": "mlp.up", "down": "mlp.down"}})
             ff_norm = norm("norm2", "hc2")
+        params = {"streams": n}
         if hyper:
-            layers.append(LayerSpec(prefix=prefix, mixer=mixer, feed_forward=ff, mixer_norm=norm("norm1", "hc1"), feed_forward_norm=ff_norm,
-                                    block="hyper_connections",
-                                    params={"streams": n, "mixer_hc": {"out": "hc1.out", "mix": "hc1.mix"},
-                                            "feed_forward_hc": {"out": "hc2.out", "mix": "hc2.mix"}}))
-        else:
-            layers.append(LayerSpec(prefix=prefix, mixer=mixer, feed_forward=ff, mixer_norm=norm("norm1", "hc1"), feed_forward_norm=ff_norm,
-                                    block="prenorm_residual"))
+            params.update({"mixer_hc": {"out": "hc1.out", "mix": "hc1.mix"}, "feed_forward_hc": {"out": "hc2.out", "mix": "hc2.mix"}})
+        layers.append(LayerSpec(prefix=prefix, mixer=mixer, feed_forward=ff, mixer_norm=norm("norm1", "hc1"), feed_forward_norm=ff_norm,
+                                block="hyper_connections", params=params))
     return ModelSpec(
         architecture="Keralix", vocab_size=cfg.vocab, hidden_size=W,
         embedding=PartSpec("token_table", {"vocab": cfg.vocab, "width": W, "name": "embed", "scale": cfg.embedding_scale, "copies": n}),

@@ -302,8 +302,9 @@ class HyperConnectionBlock(Block):
     the name of a; layer.params: "streams" (n), "mixer_hc" and "feed_forward_hc" ({"out": name of b, "mix": name of M}).
     Sublayers write their output into a float32 buffer (forward(..., accumulate=False)).  The update of the copies is left
     to the next reader of the stream: the next sublayer's norm (of this block or of the one after it) mixes, adds and norms
-    in one pass.  As the model's last block the feed-forward runs on the wanted rows only.  n = 1 with a = b = M = 1 is the
-    plain pre-norm block."""
+    in one pass.  As the model's last block the feed-forward runs on the wanted rows only.  Without "mixer_hc" /
+    "feed_forward_hc" no tensors are read and b and M are ones: with n = 1 that is the plain pre-norm block
+    x <- x + f(norm(x)), for layers with or without a feed-forward."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -313,7 +314,10 @@ class HyperConnectionBlock(Block):
         self.mixer = make_part("mixer", spec.mixer, prefix, rt)
         self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt) if spec.feed_forward is not None else None
         self.ff_norm = make_part("norm", spec.feed_forward_norm, prefix, rt) if self.ff is not None else None
-        self.hc_names = [dict(spec.params["mixer_hc"])] + ([dict(spec.params["feed_forward_hc"])] if self.ff is not None else [])
+        names = [spec.params.get("mixer_hc")] + ([spec.params.get("feed_forward_hc")] if self.ff is not None else [])
+        self.hc_names = [dict(x) if x else None for x in names]
+        if any(x is None for x in self.hc_names) and self.n != 1:
+            raise ValueError("hyper-connection block: several copies of the stream need their mixing tensors")
         self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff) if p is not None)
         self.graph_safe = all(p.graph_safe for p in self.parts)
         self.picks_rows = True
@@ -324,14 +328,18 @@ class HyperConnectionBlock(Block):
         n = self.n
         specs = [w for p in self.parts for w in p.weight_specs()]
         for names in self.hc_names:
-            specs += [WeightSpec(self.prefix + names["out"], ((n,),), role="vector", init=("uniform", 0.5, 1.0)),
-                      WeightSpec(self.prefix + names["mix"], ((n, n),), role="vector", init=("uniform", 0.0, 0.6))]
+            if names is not None:
+                specs += [WeightSpec(self.prefix + names["out"], ((n,),), role="vector", init=("uniform", 0.5, 1.0)),
+                          WeightSpec(self.prefix + names["mix"], ((n, n),), role="vector", init=("uniform", 0.0, 0.6))]
         return specs
 
     def bind(self, tensors):
         for p in self.parts:
             p.bind(tensors)
-        self.hc = [(tensors[self.prefix + names["mix"]].contiguous(), tensors[self.prefix + names["out"]]) for names in self.hc_names]
+        import torch
+        one = torch.ones(1, dtype=torch.float32, device=self.rt.device)
+        self.hc = [(one, one) if names is None else (tensors[self.prefix + names["mix"]].contiguous(), tensors[self.prefix + names["out"]])
+                   for names in self.hc_names]
 
     def cache_specs(self):
         return self.mixer.cache_specs()

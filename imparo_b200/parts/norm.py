@@ -26,6 +26,7 @@ class RMSNorm(Part):
         self.name = prefix + params["name"]
         self.offset = float(params.get("offset", 0.0))
         self.streams = int(params.get("streams") or 1)
+        self.by_copies = params.get("streams") is not None       # the stream is laid out in copies (even one): the copies' kernel reads it
         self.coef_name = prefix + params["stream_weights"] if params.get("stream_weights") else None
         self.weight: Optional[torch.Tensor] = None
         self.coef: Optional[torch.Tensor] = None
@@ -50,7 +51,7 @@ class RMSNorm(Part):
         many of them.  Returns activations in the path's dtype."""
         n = x.shape[0] if rows is None else int(n_rows if n_rows is not None else rows.numel())
         out = self.rt.workspace.get(tag, (n, self.width), self.rt.act_dtype, first="tokens" if rows is None else "rows")
-        if self.streams > 1 or self.coef is not None:
+        if self.by_copies:
             ops.streams_norm(x, self.streams, self.coef, self.weight, self.eps, out, rows)
         else:
             ops.rmsnorm(x, self.weight, self.eps, out, rows)

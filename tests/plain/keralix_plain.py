@@ -198,7 +198,7 @@ def forward(cfg, W, tokens, dtype=np.float64, layer_sums=None):
     W = {k: np.asarray(v, dtype=dtype) for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     n = int(cfg.get("streams") or 1)
-    e = W["embed"][np.asarray(tokens)] * dtype(cfg["embedding"]["scale"])
+    e = W["embed"][np.asarray(tokens)] * dtype((cfg.get("embedding") or {}).get("scale", 1.0))
     X = np.stack([e] * n)
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
