@@ -21,8 +21,8 @@ captured for its shape, as every step whose shape repeats is.
 continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 32-bit) and
 print one JSON line each; --workload sizes runs the headline's model at further prompt lengths
 and decode contexts; --workload vipotar / negotar run the Vipotar / Negotar design at two sizes that resemble a real model's layers beside
-LFM2 at equal width, depth, heads and feed-forward size (prefill of one prompt, decode at batch 8); the default is the
-headline above.
+LFM2 at equal width, depth, heads and feed-forward size (prefill of one prompt, decode at batch 8), --workload keralix the
+Keralix design beside Vipotar likewise; the default is the headline above.
 """
 import argparse
 import json
@@ -425,6 +425,110 @@ def workload_negotar(args):
     return 0
 
 
+def keralix_config(width, layers, streams, heads, kv_heads, head, window, lat_heads, lat_dim, lat_vdim, q_rank, kv_rank,
+                   delta_heads, delta_kv_heads, delta_dim, delta_vdim, inner, ff, vocab):
+    """A Keralix config.json of the given sizes: layers in the order delta rule, windowed attention, latent attention, latent
+    attention, each with a dense feed-forward; `streams` copies of the stream; half of each attention head rotated; scores
+    capped at 50; four conv taps."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "conv": 4, "scale": head ** -0.5, "softcap": 50.0,
+            "mask": {"size": window}, "rot": {"dims": head // 2, "base": 1000000.0}}
+    latent = {"heads": lat_heads, "dim": lat_dim, "vdim": lat_vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": lat_dim ** -0.5}
+    delta = {"heads": delta_heads, "kv_heads": delta_kv_heads, "dim": delta_dim, "vdim": delta_vdim, "conv": 4,
+             "decay_rank": inner, "gate_rank": inner}
+    kinds = [("channel_delta", delta), ("attention", attn), ("latent_attention", latent), ("latent_attention", latent)]
+    return {"architecture": "Keralix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": streams,
+            "embedding": {"scale": float(width) ** 0.5},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]}
+
+
+def workload_keralix(args):
+    """Keralix at two sizes beside Vipotar (windowed attention next to a recurrent linear attention, dense feed-forward: the
+    closest design the engine serves) at equal width, depth, attention heads, window, recurrent state size and feed-forward
+    size: prefill of one prompt of 512 and 2,048 tokens, decode steps of 8 requests with 2,048 positions each.  Rooflines:
+    prefill against the measured bfloat16 peak with the flops the design needs (products over all tokens, attention over
+    the window, the latent attention in its latent space over all earlier positions, the delta rule's 7 * heads * dim * vdim
+    per token); decode against the measured copy bandwidth with the bytes a step must move (every matrix once, the windows'
+    keys, the latents, the recurrent states read and written)."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    sizes = {"width1024": dict(width=1024, layers=8, streams=4, heads=16, kv_heads=4, head=64, window=512, lat_heads=16, lat_dim=64,
+                               lat_vdim=64, q_rank=384, kv_rank=128, delta_heads=8, delta_kv_heads=4, delta_dim=64, delta_vdim=128,
+                               inner=64, ff=4096, vocab=32768),
+             "width2048": dict(width=2048, layers=8, streams=4, heads=32, kv_heads=8, head=64, window=1024, lat_heads=32, lat_dim=64,
+                               lat_vdim=64, q_rank=768, kv_rank=256, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
+                               inner=128, ff=8192, vocab=65536)}
+    out = {"metric": "Keralix beside Vipotar at equal sizes: prefill of one prompt, decode at batch 8 with 2,048 positions",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name, z in sizes.items():
+            row = {}
+            W, L, F, V = z["width"], z["layers"], z["ff"], z["vocab"]
+            for model in ("keralix", "vipotar"):
+                if model == "keralix":
+                    cfg = keralix_config(**z)
+                    n_delta, n_attn = (L + 3) // 4, (L + 2) // 4
+                    n_lat = L - n_delta - n_attn
+                    H, G, D = z["heads"], z["kv_heads"], z["head"]
+                    LH, LD, LV, QR, R = z["lat_heads"], z["lat_dim"], z["lat_vdim"], z["q_rank"], z["kv_rank"]
+                    DH, DG, DD, DV, I = z["delta_heads"], z["delta_kv_heads"], z["delta_dim"], z["delta_vdim"], z["inner"]
+                    attn = (H + G) * D * W + W * H * D
+                    lat = (QR + R + LH * LV) * W + LH * LD * QR + LH * LD * R + LH * LV * R + W * LH * LV
+                    delta = (2 * DG * DD + DH * DV + DH + 2 * I) * W + DH * DD * I + DH * DV * I + W * DH * DV
+                    matrix = n_attn * attn + n_lat * lat + n_delta * delta + L * 3 * W * F
+                    state = n_delta * DH * DD * DV * 4
+
+                    def flops(T):
+                        keys = sum(min(t + 1, z["window"]) for t in range(T))
+                        return (2.0 * T * matrix + 2.0 * V * W + n_attn * 4.0 * H * D * keys + n_lat * 4.0 * LH * R * T * (T + 1) / 2
+                                + n_delta * 7.0 * DH * DD * DV * T)
+
+                    def step_bytes(batch, ctx):
+                        per_request = 2 * state + n_attn * min(ctx, z["window"]) * G * D * 2 + n_lat * ctx * R * 2
+                        return (matrix + V * W) * 2 + batch * per_request
+                    params = matrix + V * W
+                else:
+                    v = dict(width=W, layers=L, heads=z["heads"], kv_heads=z["kv_heads"], head=z["head"], window=z["window"],
+                             lin_heads=z["delta_heads"], lin_dim=z["delta_dim"], lin_vdim=z["delta_vdim"], ff=F, vocab=V)
+                    cfg = vipotar_config(**v)
+                    qkv = (v["heads"] + 2 * v["kv_heads"]) * v["head"] * W + W * v["heads"] * v["head"]
+                    lin = (2 * v["lin_heads"] * v["lin_dim"] + 2 * v["lin_heads"] * v["lin_vdim"]) * W + W * v["lin_heads"] * v["lin_vdim"]
+                    matrix = L * (qkv + lin + 2 * W * F)
+                    state = L * v["lin_heads"] * v["lin_dim"] * v["lin_vdim"] * 4
+                    kv_tok = L * 2 * v["kv_heads"] * v["head"] * 2
+
+                    def flops(T):
+                        keys = sum(min(t + 1, v["window"]) for t in range(T))
+                        return 2.0 * T * matrix + 2.0 * V * W + L * (4.0 * v["heads"] * v["head"] * keys
+                                                                     + 4.0 * v["lin_heads"] * v["lin_dim"] * v["lin_vdim"] * T)
+
+                    def step_bytes(batch, ctx):
+                        return (matrix + V * W) * 2 + batch * (2 * state + min(ctx, v["window"]) * kv_tok)
+                    params = matrix + 2 * V * W
+                engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=8, page_size=PAGE, max_step_tokens=PROMPT,
+                                random_init={"norm_jitter": 0.0})
+                r = {"params": params, "prefill": {}}
+                for T in (512, 2048):
+                    ms = measure_prefill(engine, reps=5, warmup=3, rng=rng, prompt=T)
+                    r["prefill"][str(T)] = {"value": round(T * 1000.0 / ms, 1), "ms": round(ms, 3),
+                                            "frac": round(flops(T) / (ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+                ms, launches, library, ctx = measure_decode(engine, 8, max(20, args.steps // 4), max(args.warmup, 3), rng, prompt=PROMPT)
+                nbytes = step_bytes(8, ctx)
+                r["decode_b8"] = {"value": round(8 * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "own_kernels_per_step": round(launches, 1),
+                                  "library_gemms_per_step": round(library, 1), "bytes_per_step": int(nbytes),
+                                  "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                row[model] = r
+                del engine
+                torch.cuda.empty_cache()
+            out["sizes"][name] = dict(row, config=z)
+    out["peaks"] = pk["source"]
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def _preset(name):
     with open(os.path.join(ROOT, "imparo_b200", "config", "presets", name + ".json")) as f:
         return json.load(f)
@@ -643,7 +747,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar", "keralix"],
                     help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit.  "
@@ -673,6 +777,8 @@ def main():
         return workload_vipotar(args)
     if args.workload == "negotar":
         return workload_negotar(args)
+    if args.workload == "keralix":
+        return workload_keralix(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

@@ -297,6 +297,8 @@ struct QkvSource {
     __nv_bfloat16* k_out;       // the caches, writable
     __nv_bfloat16* v_out;
     float softcap;              // c > 0: the scaled score becomes c * tanh(score / c) (with or without the fields above)
+    int kv_groups;              // > 1: that many groups of query heads in a row read the SAME cached head (the launch's
+                                // nkv counts groups; the cache rows hold nkv / kv_groups heads).  Not with the fields above.
 };
 
 template <int HD, bool FROM_QKV>
@@ -337,7 +339,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int h0 = kvh * G;
     const size_t part_base = ((size_t)t * nh + h0) * n_splits + split;         // + g * n_splits
     const int* tab = table + (size_t)item_of_token[t] * max_blocks;
-    const size_t kvw = (size_t)nkv * HD;
+    const int kvg = (!FROM_QKV && src.kv_groups > 1) ? src.kv_groups : 1;
+    const size_t kvw = (size_t)(nkv / kvg) * HD;
+    const int kv_col = (kvh / kvg) * HD;                               // where this group's cached head starts in a row
     const int kb_first = begin / KEYS, kb_last = (end - 1) / KEYS;
     // A thread fetches half a row of the tile (two threads per key): one page lookup, then CH / 2
     // 16-byte pieces each of the key and of the value.  The two threads of a key take alternate
@@ -361,7 +365,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 rowi = (size_t)page * page_size + within;
             }
         }
-        const size_t off = rowi * kvw + (size_t)kvh * HD + c0 * 8;
+        const size_t off = rowi * kvw + (size_t)kv_col + c0 * 8;
         uint8_t* const kd = k_s(buf);
         uint8_t* const vd = v_s(buf);
 #pragma unroll
@@ -685,9 +689,10 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
                              const int* table, int max_blocks, int page_size, int n_pages,
                              int window, float scale, void* out, float* part_acc, float* part_ml,
                              int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh, int overlap_prev,
-                             int* status, cudaStream_t stream, float softcap = 0.f) {
+                             int* status, cudaStream_t stream, float softcap = 0.f, int kv_groups = 1) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
+    if (kv_groups < 1 || nkv % kv_groups != 0 || (kv_groups > 1 && qkv_src != nullptr)) return -5;
     if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
     // at most 2048 splits (the ordered combine keeps one pair per split in shared memory), and the
     // chunks must cover every position a table of this width can hold; refused before any launch
@@ -709,6 +714,7 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
     const bool from_qkv = qkv_src != nullptr;
     pf::QkvSource none{};
     none.softcap = softcap > 0.f ? softcap : 0.f;
+    none.kv_groups = kv_groups;
     const pf::QkvSource& src = from_qkv ? *qkv_src : none;
 #define IMPARO_DECODE(HD_, F_) launch(pf::attn_decode_mma_kernel<HD_, F_>, grid, dim3(pf::THREADS), smem, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, \
@@ -742,6 +748,20 @@ extern "C" int imparo_attention_decode_mma_capped(const void* q, const void* k_c
     return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
                              scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, overlap_prev ? 1 : 0,
                              status, stream, softcap);
+}
+
+// The same for query heads in `kv_groups` groups per cached head: nkv counts the groups (nh / nkv <= 8 heads each), the cache
+// rows hold nkv / kv_groups heads of hd.  An attention whose heads all share one cached row per position (keys and values
+// made from one latent) runs as kv_groups = nkv groups over caches of one head.  The partials are left uncombined.
+extern "C" int imparo_attention_decode_mma_grouped(const void* q, const void* k_cache, const void* v_cache,
+                                                   const int* positions, const int* item_of_token,
+                                                   const int* table, int max_blocks, int page_size, int n_pages,
+                                                   int window, float scale, float* part_acc, float* part_ml,
+                                                   int n_tok, int nh, int nkv, int kv_groups, int hd, int chunk, int n_splits,
+                                                   int fresh, float softcap, int* status, cudaStream_t stream) {
+    return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
+                             scale, nullptr, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, 0, status, stream,
+                             softcap, kv_groups);
 }
 
 // The same for a step in which every request brings ONE token, straight from the qkv product's split partials

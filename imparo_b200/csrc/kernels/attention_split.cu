@@ -241,13 +241,15 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
 constexpr int COMBINE_MAX_SPLITS = 2048;
 template <typename T>
 __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                          T* __restrict__ out, int hd, int n_splits, int sink) {
+                                          T* __restrict__ out, int hd, int n_splits, int sink,
+                                          const float* __restrict__ sink_values, int nh) {
     __shared__ float f_s[COMBINE_MAX_SPLITS];             // exp(max_s - M), 0 for an empty split
     __shared__ float l_s[COMBINE_MAX_SPLITS];
     __shared__ float m_all;
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;                         // token * nh + head
+    const float sink_at = sink_values ? sink_values[th % nh] : 0.f;      // the extra term's score: 0, or a number per head
     const float* ml = part_ml + th * n_splits * 2;
     const float* acc = part_acc + th * n_splits * hd;
     const int d0 = threadIdx.x;
@@ -264,7 +266,7 @@ __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, co
         float M = -INFINITY;
         for (int s = threadIdx.x; s < n_splits; s += 32) if (l_s[s] > 0.f) M = fmaxf(M, f_s[s]);
         M = warp_max(M);
-        if (sink) M = fmaxf(M, 0.f);                      // one more term of score 0 (sum 1, no value) takes part in the fold
+        if (sink) M = fmaxf(M, sink_at);                  // one more term (sum 1, no value) takes part in the fold
         if (threadIdx.x == 0) m_all = M;
     }
     __syncthreads();
@@ -272,7 +274,7 @@ __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, co
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) f_s[s] = l_s[s] > 0.f ? expf(f_s[s] - M) : 0.f;
     __syncthreads();
     for (int d = d0; d < hd; d += blockDim.x) {
-        float a = 0.f, L = sink ? expf(-M) : 0.f;
+        float a = 0.f, L = sink ? expf(sink_at - M) : 0.f;
         for (int s0 = 0; s0 < n_splits; s0 += 16) {
             if (s0 > 0 || d != d0) {
 #pragma unroll
@@ -355,9 +357,9 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
     if (out == nullptr) return 0;               // the partials stay in scratch for a consumer that combines them itself
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == IMPARO_DT_F32)
-        launch(attn_split_combine_kernel<float>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits, 0);
+        launch(attn_split_combine_kernel<float>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits, 0, (const float*)nullptr, 1);
     else
-        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits, 0);
+        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits, 0, (const float*)nullptr, 1);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
@@ -370,9 +372,28 @@ extern "C" int imparo_attention_split_combine(const float* part_acc, const float
     if (n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return -2;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == IMPARO_DT_F32)
-        launch(attn_split_combine_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits, sink);
+        launch(attn_split_combine_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits, sink, (const float*)nullptr, 1);
     else if (dtype == IMPARO_DT_BF16)
-        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits, sink);
+        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits, sink, (const float*)nullptr, 1);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// The combine with one more term in the denominator whose score is a number per head (sink_values [nh], in the units of
+// the scaled scores; rows are token * nh + head).
+extern "C" int imparo_attention_split_combine_sinks(const float* part_acc, const float* part_ml, void* out, int dtype,
+                                                    int n_rows, int hd, int n_splits, const float* sink_values, int nh,
+                                                    cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_splits < 1 || n_splits > COMBINE_MAX_SPLITS || sink_values == nullptr || nh < 1) return -2;
+    const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    if (dtype == IMPARO_DT_F32)
+        launch(attn_split_combine_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits, 1,
+               sink_values, nh);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out,
+               hd, n_splits, 1, sink_values, nh);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

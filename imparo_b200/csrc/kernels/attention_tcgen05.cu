@@ -96,6 +96,8 @@ struct Args {
     int late_trigger;        // the next kernel runs beside this one and must find all before this one complete (common.cuh)
     int sink;                // the softmax's denominator counts one more term of score 0 that has no value: the running max
                              // starts at 0 and the running sum at 1, as if a key of score 0 had been seen before all others
+    const float* sink_values;  // with sink: the extra term's score per query head, in the units of the SCALED scores (it is
+                             // not scaled itself); null: 0 for every head
     float softcap;           // c > 0: the scaled score becomes c * tanh(score / c).  The raw product v is replaced by
                              // (c / scale) * tanh(v * scale / c) as soon as it is read, so that everything after it (the
                              // max, which commutes with a rising function, and the exponent) stays as it is
@@ -292,7 +294,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         float o[DH];
 #pragma unroll
         for (int d = 0; d < DH; ++d) o[d] = 0.f;
-        float m_run = a.sink ? 0.f : -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f, corr_prev = 0.f;
+        const float sink2 = (a.sink && a.sink_values) ? a.sink_values[head] * 1.4426950408889634f : 0.f;     // in units of log2(e)
+        float m_run = a.sink ? sink2 : -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f, corr_prev = 0.f;
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
         const bool capped = a.softcap > 0.f;
         const float cap_in = capped ? a.scale / a.softcap : 0.f, cap_out = capped ? a.softcap / a.scale : 0.f;
@@ -770,7 +773,8 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(q_ready);
         }
-        float m_used = -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f;       // (the sink's 1 is in units of max 0: see j == 0)
+        const float sink2 = (a.sink && a.sink_values) ? a.sink_values[head] * 1.4426950408889634f : 0.f;     // in units of log2(e)
+        float m_used = -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f;       // (the sink's 1 is in units of its own score: see j == 0)
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
         const bool capped = a.softcap > 0.f;
         const float cap_in = capped ? a.scale / a.softcap : 0.f, cap_out = capped ? a.softcap / a.scale : 0.f;
@@ -830,8 +834,8 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // the max in use stays unless it would be exceeded by more than PP_GROW somewhere in the warp
             float m_new, corr = 1.f;
             if (j == 0) {
-                m_new = a.sink ? fmaxf(m_row, 0.f) : m_row;
-                if (a.sink) corr = ex2(-m_new);                              // the sink's share of the sum, brought to the max in use
+                m_new = a.sink ? fmaxf(m_row, sink2) : m_row;
+                if (a.sink) corr = ex2(sink2 - m_new);                       // the sink's share of the sum, brought to the max in use
             } else {
                 const bool grow = m_row > m_used + PP_GROW;                  // (true for m_used = -inf and a finite m_row)
                 const bool rescale = __any_sync(0xffffffffu, grow);
@@ -964,6 +968,14 @@ static int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a
 
 using namespace imparo;
 
+// The same with the extra term's score given per query head (sink_values [nh], unscaled, with mode bit 2; null: 0), for up
+// to 128 query heads per kv head: a tile then holds 128 / G tokens, down to one.
+extern "C" int imparo_attention_prefill_tc_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int* item_row_start, const int* item_start_pos, int n_items,
+                                                 const int* table, int max_blocks, int page_size, int n_pages,
+                                                 int window, float scale, float softcap, const float* sink_values, void* out,
+                                                 int n_tok, int nh, int nkv, int hd, int mode, int* status, cudaStream_t stream);
+
 // bfloat16, head size 64 or 128, at most 8 query heads per kv head, pages of 16, 32, 64 or 128
 // positions; else -8 (the caller uses another kernel).  mode bit 0: at head size 64 the kernel that gives a CTA two
 // query tiles in turn (else, and at head size 128, one tile per CTA); bit 1: the kernel lets its dependents come only
@@ -974,11 +986,20 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, float softcap, void* out, int n_tok, int nh, int nkv, int hd,
                                            int mode, int* status, cudaStream_t stream) {
+    return imparo_attention_prefill_tc_sinks(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, max_blocks, page_size,
+                                             n_pages, window, scale, softcap, nullptr, out, n_tok, nh, nkv, hd, mode, status, stream);
+}
+
+extern "C" int imparo_attention_prefill_tc_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int* item_row_start, const int* item_start_pos, int n_items,
+                                                 const int* table, int max_blocks, int page_size, int n_pages,
+                                                 int window, float scale, float softcap, const float* sink_values, void* out,
+                                                 int n_tok, int nh, int nkv, int hd, int mode, int* status, cudaStream_t stream) {
     const int two_tiles = mode & 1;
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     const int G = nh / nkv;
-    if (G > 8 || (hd != 64 && hd != 128)) return -8;
+    if (G > fa::ROWS || (hd != 64 && hd != 128)) return -8;
     if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return -8;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return -8;
     if (!(scale > 0.f)) return -8;                           // the row max is taken before the scaling
@@ -998,6 +1019,7 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.nh = nh; a.nkv = nkv; a.scale = scale;
     a.late_trigger = (mode >> 1) & 1;
     a.sink = (mode >> 2) & 1;
+    a.sink_values = a.sink ? sink_values : nullptr;
     a.softcap = softcap > 0.f ? softcap : 0.f;
     if (hd == 64 && two_tiles) {
         // two tiles per CTA: half as many CTAs along y (an upper bound again)

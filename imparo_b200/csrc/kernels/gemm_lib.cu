@@ -38,25 +38,52 @@ extern "C" int imparo_gemm_lib_init(void* workspace, size_t workspace_bytes) {
     return 0;
 }
 
+// The handle follows the stream of the call.  Setting the stream resets the library's workspace to its own, so both are
+// set together, and only when the stream changes (a step issues dozens of products on one stream).
+static int bind_stream(cudaStream_t stream) {
+    if (g_bound && g_bound_stream == stream) return 0;
+    cublasStatus_t s = cublasSetStream(g_handle, stream);
+    if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+    if (g_workspace) {
+        s = cublasSetWorkspace(g_handle, g_workspace, g_workspace_bytes);
+        if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+    }
+    g_bound = true;
+    g_bound_stream = stream;
+    return 0;
+}
+
+// One product per head, all in one call: out[m, h, :] = W[h] x[m, h, :] for h < heads, with x rows of lda elements holding
+// heads * K, W [heads, N, K] and out rows of ldc elements holding heads * N (bfloat16 in and out, 32-bit sums).
+extern "C" int imparo_gemm_bf16_heads(const void* A, const void* W, void* C, int M, int heads, int N, int K, int lda, int ldc,
+                                      cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || heads <= 0) return 0;
+    if (!g_handle) return -1;
+    int rc = bind_stream(stream);
+    if (rc) return rc;
+    const float alpha = 1.f, beta = 0.f;
+    // column-major view per head: C_h^T[N,M] = W_h[N,K] * A_h^T[K,M]
+    cublasStatus_t s = cublasGemmStridedBatchedEx(g_handle, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha,
+                                                  W, CUDA_R_16BF, K, (long long)N * K, A, CUDA_R_16BF, lda, (long long)K, &beta,
+                                                  C, CUDA_R_16BF, ldc, (long long)N, heads, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+#ifdef IMPARO_TIMELINE
+    launch(imparo::library_product_done_kernel, dim3(1), dim3(32), 0, stream);
+#endif
+    return 0;
+}
+
 // c_dtype: 0 = float32 out, 1 = bfloat16 out.  accumulate adds into C (32-bit C only).
 extern "C" int imparo_gemm_bf16_nt(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
                                    int lda, int ldc, int accumulate, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!g_handle) return -1;
     if (accumulate && c_dtype != IMPARO_DT_F32) return -2;
-    cublasStatus_t s;
-    if (!g_bound || g_bound_stream != stream) {
-        // setting the stream resets the library's workspace to its own, so both are set together,
-        // and only when the stream changes (a step issues dozens of products on one stream)
-        s = cublasSetStream(g_handle, stream);
-        if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
-        if (g_workspace) {
-            s = cublasSetWorkspace(g_handle, g_workspace, g_workspace_bytes);
-            if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
-        }
-        g_bound = true;
-        g_bound_stream = stream;
+    {
+        const int rc = bind_stream(stream);
+        if (rc) return rc;
     }
+    cublasStatus_t s;
     const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
     // column-major view: C^T[N,M] = W[N,K] * A^T[K,M]
     s = cublasGemmEx(g_handle, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha,

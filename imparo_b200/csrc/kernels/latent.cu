@@ -90,9 +90,37 @@ heads_linear_kernel(const T* __restrict__ x, size_t x_stride, const T* __restric
     }
 }
 
+// x[t, c] *= sigmoid(gate[t, c]) in place (gate: columns of a 32-bit product), eight columns per thread where they align
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ x, size_t x_stride, const float* __restrict__ gate, size_t gate_stride, int n_tok, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    T* xr = x + (size_t)t * x_stride;
+    const float* gr = gate + (size_t)t * gate_stride;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x)
+        xr[c] = from_f32<T>(to_f32(xr[c]) * (1.0f / (1.0f + expf(-gr[c]))));
+}
+
 }  // namespace imparo
 
 using namespace imparo;
+
+// x: rows of x_stride elements (width used), bfloat16 or float32; gate: float32 rows of gate_stride floats.
+extern "C" int imparo_sigmoid_gate(void* x, long long x_stride, const float* gate, long long gate_stride, int dtype, int n_tok,
+                                   int width, cudaStream_t stream) {
+    if (n_tok <= 0 || width <= 0) return 0;
+    const dim3 grid((width + 255) / 256 > 8 ? 8 : (width + 255) / 256, n_tok);
+    if (dtype == IMPARO_DT_F32)
+        launch(sigmoid_gate_kernel<float>, grid, dim3(256), 0, stream, (float*)x, (size_t)x_stride, gate, (size_t)gate_stride, n_tok, width);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(sigmoid_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, (size_t)x_stride, gate,
+               (size_t)gate_stride, n_tok, width);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
 
 // proj: float32 rows of `stride` floats; q_out: [n_tok, q_rank] and cache pages of c_rank per position, both in dtype.
 extern "C" int imparo_latent_norm_store(const float* proj, long long stride, int q_off, int q_rank, int c_off, int c_rank,

@@ -91,6 +91,13 @@ def _declare_kernels(lib):
              [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_decode_mma_capped",
              [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, c_float, P, S])
+    _declare(lib, "imparo_attention_decode_mma_grouped",
+             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, I, I, I, I, I, I, I, I, c_float, P, S])
+    _declare(lib, "imparo_attention_split_combine_sinks", [P, P, P, I, I, I, I, P, I, S])
+    _declare(lib, "imparo_attention_prefill_tc_sinks",
+             [P, P, P, P, P, I, P, I, I, I, I, c_float, c_float, P, P, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_gemm_bf16_heads", [P, P, P, I, I, I, I, I, I, S])
+    _declare(lib, "imparo_sigmoid_gate", [P, c_int64, P, c_int64, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma_qkv",
              [P, I, c_int64, P, P, P, I, c_float, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",

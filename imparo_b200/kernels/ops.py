@@ -651,6 +651,51 @@ def attention_split_combine(part_acc, part_ml, out, n_rows, hd, n_splits, sink: 
                                                          n_splits, int(bool(sink)), _stream()), "attention_split_combine")
 
 
+def head_groups(nh: int, nkv: int, most: int = 8) -> int:
+    """Into how many groups the query heads of one kv head are cut so that a group has at most `most` heads: the fewest
+    that divide them evenly (1 when they fit as they are)."""
+    per = nh // nkv
+    for g in range(1, per + 1):
+        if per % g == 0 and per // g <= most:
+            return g
+    return per
+
+
+def paged_attention_split_shared(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
+                                 out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, fresh: int = 0,
+                                 softcap: float = 0.0, sink_values: Optional[torch.Tensor] = None) -> bool:
+    """Split-key attention on tensor cores for any number of query heads per kv head: the heads of a kv head are cut into
+    groups of at most 8 (head_groups), each group a CTA row of its own over the same cached head, so an attention whose
+    heads all share one cached row per position (nkv = 1) still spreads over heads x key chunks CTAs.  Then the ordered
+    combine, with one more term per head in the denominator when sink_values (float32 [nh], unscaled scores) is given.
+    bfloat16, head size 64 or 128, chunk >= 64; returns False, having launched nothing, for other shapes."""
+    if not (q.dtype == torch.bfloat16 and hd in (64, 128) and chunk >= 64):
+        return False
+    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status, sink_values)
+    T = q.shape[0]
+    groups = head_groups(nh, nkv)
+    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "paged_attention_split_shared: q/out shapes")
+    _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _need(part_acc.dtype == torch.float32 and part_acc.numel() >= T * nh * n_splits * hd
+          and part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * n_splits * 2, "split scratch too small")
+    _need(T <= 65535 and 1 <= n_splits <= MAX_SPLITS and chunk * n_splits >= table.shape[1] * page_size,
+          "paged_attention_split_shared: tokens, chunks and their cover of the block table")
+    _need(sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == nh), "sink values float32 [heads]")
+    _check(_lib.kernels().imparo_attention_decode_mma_grouped(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table), table.shape[1], page_size,
+        n_pages, int(window or 0), float(scale), _ptr(part_acc), _ptr(part_ml), T, nh, nkv * groups, groups, hd, int(chunk),
+        int(n_splits), int(fresh), float(softcap or 0.0), _ptr(status), _stream()), "attention_decode_mma_grouped")
+    if sink_values is not None:
+        _check(_lib.kernels().imparo_attention_split_combine_sinks(_ptr(part_acc), _ptr(part_ml), _ptr(out), _code(out), T * nh, hd,
+                                                                   n_splits, _ptr(sink_values), nh, _stream()),
+               "attention_split_combine_sinks")
+    else:
+        attention_split_combine(part_acc, part_ml, out, T * nh, hd, n_splits)
+    return True
+
+
 def _parts_of(x):
     """(pointer tensor, parts, stride) of a kernel input that is a tensor or a PartialProduct."""
     if isinstance(x, PartialProduct):
@@ -844,7 +889,7 @@ def attention_decode_from_qkv(qkv, positions, item_of_token, q_w, k_w, inv_freq,
 
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
                       scale, out, nh, nkv, hd, status, kernel: str = "auto", dependents_after_wait: bool = False,
-                      sink: bool = False, softcap: float = 0.0):
+                      sink: bool = False, softcap: float = 0.0, sink_values: Optional[torch.Tensor] = None, max_group: int = 8):
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
     query heads per kv head).  Returns False, having launched nothing, for other shapes.
 
@@ -858,14 +903,19 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
 
     sink: the softmax's denominator counts one more term of score 0 that has no value (the tcgen05 kernels only;
     where they decline the result is False).  softcap c > 0: the scaled score becomes c * tanh(score / c) (the tcgen05
-    kernels only, likewise)."""
-    if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
+    kernels only, likewise).  sink_values: float32 [nh], the extra term's score per head, unscaled (implies sink).
+
+    max_group: the most query heads per kv head the caller wants on this kernel (the tcgen05 kernels take up to 128: a tile
+    is 128 / group tokens of the group's heads, which pays when all heads share one cached row; the mma kernel takes 8)."""
+    if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > min(max_group, 128):
         return False
-    only_tc = bool(sink) or bool(softcap)      # variants that only the tcgen05 kernels have
+    sink = bool(sink) or sink_values is not None
+    only_tc = sink or bool(softcap) or nh // nkv > 8      # variants that only the tcgen05 kernels have
     if only_tc and kernel == "auto" and _S.switches.attn_prefill == "mma":
         return False
-    _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status)
+    _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status, sink_values)
     T = q.shape[0]
+    _need(sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == nh), "attention_prefill: sink values float32 [heads]")
     _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "attention_prefill: q/out shapes")
     _need(q.is_contiguous() and out.is_contiguous(), "attention_prefill: q and out must be dense")
     _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
@@ -885,8 +935,8 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
         # part of the step's shape
         two_tiles = kernel == "tcgen05" or (kernel == "auto" and table.shape[1] * page_size >= 1024)
         late = bool(dependents_after_wait)      # without programmatic launches the two kernels simply run in stream order
-        rc = _lib.kernels().imparo_attention_prefill_tc(*head, float(softcap or 0.0), *tail[:-2],
-                                                        (1 if two_tiles else 0) | (2 if late else 0) | (4 if sink else 0), *tail[-2:])
+        rc = _lib.kernels().imparo_attention_prefill_tc_sinks(*head, float(softcap or 0.0), _ptr(sink_values), *tail[:-2],
+                                                              (1 if two_tiles else 0) | (2 if late else 0) | (4 if sink else 0), *tail[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
             return 2 if late else True
@@ -1558,6 +1608,9 @@ def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, c
                                                    _stream()), "latent_norm_store")
 
 
+HEADS_LINEAR_LIBRARY_ROWS = 64          # from this many rows on the per-head products go to the library in one batched call
+
+
 def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
     """out[t, h, :] = w[h] x[t, h, :] for every head (w [heads, n_out, n_in]; x [T, heads * n_in], out [T, heads * n_out],
     rows dense), optionally times sigmoid(gate[t, h, :]) (float32 [T, heads * n_out], rows dense).  32-bit sums."""
@@ -1570,6 +1623,16 @@ def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Opti
           "heads_linear: shapes")
     _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (T, heads * n_out)),
           "heads_linear: gate float32 [T, heads * n_out]")
+    if x.dtype == torch.bfloat16 and T >= HEADS_LINEAR_LIBRARY_ROWS and n_in % 8 == 0 and n_out % 8 == 0 \
+            and x.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+        # many rows: one batched library product over the heads (tensor cores, 32-bit sums), then the gate in place
+        _gemm_lib_ready(x.device)
+        _check(_lib.kernels().imparo_gemm_bf16_heads(_ptr(x), _ptr(w), _ptr(out), T, heads, n_out, n_in, x.stride(0), out.stride(0),
+                                                     _stream()), "gemm_bf16_heads", "library")
+        if gate is not None:
+            _check(_lib.kernels().imparo_sigmoid_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), _code(out), T,
+                                                      heads * n_out, _stream()), "sigmoid_gate")
+        return
     _need(n_in * 32 <= 48 * 1024, "heads_linear: input size per head up to 1536")
     _check(_lib.kernels().imparo_heads_linear(_ptr(x), x.stride(0), _ptr(w), _ptr(gate), gate.stride(0) if gate is not None else 0,
                                               _ptr(out), out.stride(0), _code(x), T, heads, n_in, n_out, _stream()), "heads_linear")

@@ -77,6 +77,17 @@ class LatentAttention(Part):
     def cache_specs(self):
         return (PagedKV(1, self.kv_rank, None, None, values_are_keys=True),)
 
+    def _partials_room(self, upper_context: int, groups: int) -> int:
+        """Partial results (per head) that the split-key kernel leaves for this engine's largest step of one-token rows at
+        the longest context it allows: the scratch is made for that at once, so it does not move (and void the captured
+        graphs) when a few more requests decode."""
+        most = self.rt.workspace.most
+        rows = most.get("rows", 0)
+        if not rows:
+            return 0
+        context = max(int(upper_context), min(most.get("context", 0), 1 << 17))
+        return (8 * ops.sm_count() + rows * groups * (1 + -(-context // 512))) * -(-self.heads // groups)
+
     def forward(self, x, batch, caches, residual, accumulate=True):
         kv = caches[0]
         rt, T = self.rt, x.shape[0]
@@ -95,8 +106,34 @@ class LatentAttention(Part):
         ql = ws.get("latent_ql", (T, H * R), rt.act_dtype, first="tokens")
         ops.heads_linear(q, self.w_ukT, ql)
         ol = ws.get("latent_ol", (T, H * R), rt.act_dtype, first="tokens")
-        ops.attention_any(ql, kv.k, kv.k, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, None, self.scale,
-                          self.sink, ol, H, 1, R, R, rt.status, sink_values=self.sinks)
+        done = False
+        if rt.act_dtype == torch.bfloat16 and R in (64, 128) and T <= 65535:
+            # latents of a tensor-core head size: prompt portions on the tcgen05 kernel (a tile is 128 / heads tokens times all
+            # heads over the one cached row per position), rows of one token (and portions too short for a tile, or pages that
+            # kernel does not take) on the split-key kernel with the heads in groups of at most 8
+            n1 = getattr(batch, "n_single", 0)            # decode rows come first when the step also holds portions
+            first_split = T
+            if batch.max_tokens_per_item >= 8:
+                a = n1 if 0 < n1 < batch.n_items else 0
+                if ops.attention_prefill(ql, kv.k, kv.k, batch.item_row_start[a:], batch.item_start_pos[a:], batch.n_items - a,
+                                         table[a:], kv.page_size, kv.n_pages, None, self.scale, ol, H, 1, R, rt.status,
+                                         sink_values=self.sinks, max_group=128):
+                    first_split = a
+            done = first_split == 0
+            if first_split:
+                n = first_split
+                groups = ops.head_groups(H, 1)
+                upper = table.shape[1] * kv.page_size
+                chunk, n_splits = ops.split_plan(n, groups, upper)
+                room = self._partials_room(upper, groups)
+                part_acc = ws.get("latent_part_acc", (n * H * n_splits * R,), torch.float32, reserve=room * R)
+                part_ml = ws.get("latent_part_ml", (n * H * n_splits * 2,), torch.float32, reserve=room * 2)
+                done = ops.paged_attention_split_shared(ql[:n], kv.k, kv.k, batch.positions[:n], batch.item_of_token[:n], table,
+                                                        kv.page_size, kv.n_pages, None, self.scale, ol[:n], part_acc, part_ml,
+                                                        chunk, n_splits, H, 1, R, rt.status, sink_values=self.sinks)
+        if not done:
+            ops.attention_any(ql, kv.k, kv.k, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, None,
+                              self.scale, self.sink, ol, H, 1, R, R, rt.status, sink_values=self.sinks)
         o = ws.get("latent_o", (T, hv), rt.act_dtype, first="tokens")
         ops.heads_linear(ol, self.w_uv, o, gate=proj[:, self.q_rank + R:] if self.gate else None)
         ops.linear(o, self.w_o, residual, accumulate=accumulate, status=rt.status)

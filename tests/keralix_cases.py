@@ -15,19 +15,20 @@ def latent_rows_plain(m, eps, proj, W):
     return P.latent_attention(proj, Wp, "", m, eps)
 
 
-def far_latent_case(far, seed, T=620, prompt=600):
+def far_latent_case(far, seed, T=620, prompt=600, R=16, H=2):
     """One latent at position `far` whose key points along `direction`; every other latent is orthogonal to it.  A query
     along `direction` scores `top` = 12 on it and exactly 0 on all others, so that key outweighs the hundreds of others
-    (e^12 against T) and head 0's output is its value; head 1's sink equals `top`, so it takes exactly half of the
-    weight (it counts once and is not scaled: scale is 0.5 here).  A query along -direction finds nothing: all its scores
-    are 0 or below, and head 0's sink of 8 leaves the ordinary keys a small share.
+    (e^12 against T) and an even head's output is its value; an odd head's sink equals `top`, so it takes exactly half of
+    the weight (it counts once and is not scaled: the scale is 8 / R here).  A query along -direction finds nothing: all
+    its scores are 0 or below, and the even heads' sink of 8 leaves the ordinary keys a small share.  Latent, query latent
+    and head size are all R; H heads of value size 8.
     -> (m, W, proj rows [T, q latent | kv latent | gate], seekers, blind, v_far [heads, vdim], want [T, heads * vdim])"""
     rng = np.random.default_rng(seed)
-    H, D, V, QR, R = 2, 16, 8, 16, 16
-    m = {"heads": H, "dim": D, "vdim": V, "q_rank": QR, "kv_rank": R, "scale": 0.5}
+    D, V, QR = R, 8, R
+    m = {"heads": H, "dim": D, "vdim": V, "q_rank": QR, "kv_rank": R, "scale": 8.0 / R}
     W = {"uq": np.concatenate([np.eye(D, QR)] * H), "uk": np.concatenate([np.eye(D, R)] * H) * 1.5,
          "uv": rng.standard_normal((H * V, R)) / np.sqrt(R), "dq.norm": np.ones(QR), "dkv.norm": np.ones(R),
-         "sink": np.array([8.0, 12.0])}
+         "sink": np.array([8.0, 12.0] * (H // 2))}
     direction = rng.standard_normal(R)
     direction /= np.sqrt(np.mean(direction ** 2))                       # rms 1: the norms leave it as it is
     proj = rng.standard_normal((T, QR + R + H * V))

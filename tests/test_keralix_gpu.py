@@ -376,7 +376,7 @@ def test_delta_rule_state_carries_a_far_token():
     assert np.abs(got[0] - want.reshape(420, -1)).max() <= 3e-5 * np.abs(want).max()
 
 
-def _latent_by_kernels(dtype, m, eps, proj, W, cuts, page):
+def _latent_by_kernels(dtype, m, eps, proj, W, cuts, page, tensor_cores=False):
     """The latent kernels on one request cut as `cuts`; proj: the 32-bit product [T, q latent | kv latent | gate]."""
     import torch
     from imparo_b200.kernels import ops
@@ -402,8 +402,19 @@ def _latent_by_kernels(dtype, m, eps, proj, W, cuts, page):
         ql = torch.empty(n, H * R, dtype=tdt, device="cuda")
         ops.heads_linear(q, w_ukT, ql)
         ol = torch.empty(n, H * R, dtype=tdt, device="cuda")
-        ops.attention_any(ql, cache, cache, pos, iot, table, page, n_pages, None, m["scale"], True, ol, H, 1, R, R, status,
-                          sink_values=_f32(W["sink"]))
+        sinks = _f32(W["sink"])
+        if not tensor_cores:
+            ops.attention_any(ql, cache, cache, pos, iot, table, page, n_pages, None, m["scale"], True, ol, H, 1, R, R, status,
+                              sink_values=sinks)
+        elif n >= 8 and page in (16, 32, 64, 128):
+            assert ops.attention_prefill(ql, cache, cache, _dev(np.array([0, n], dtype=np.int32)), _dev(np.array([at], dtype=np.int32)), 1,
+                                         table, page, n_pages, None, m["scale"], ol, H, 1, R, status, sink_values=sinks, max_group=128)
+        else:
+            chunk, n_splits = ops.split_plan(n, ops.head_groups(H, 1), table.shape[1] * page)
+            part_acc = torch.empty(n * H * n_splits * R, device="cuda")
+            part_ml = torch.empty(n * H * n_splits * 2, device="cuda")
+            assert ops.paged_attention_split_shared(ql, cache, cache, pos, iot, table, page, n_pages, None, m["scale"], ol, part_acc,
+                                                    part_ml, chunk, n_splits, H, 1, R, status, sink_values=sinks)
         o = torch.empty(n, H * V, dtype=tdt, device="cuda")
         ops.heads_linear(ol, w_uv, o, gate=p[:, QR + R:])
         out_all[at:at + n] = o.float().cpu().numpy()
@@ -439,21 +450,40 @@ def test_latent_attention_kernels(dtype, H, D, V, QR, R):
     assert np.abs(got - want).max() <= (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("far,page", [(0, 16), (15, 16), (16, 16), (3, 4), (31, 8)])
-def test_a_far_latent_among_hundreds_and_the_sink(dtype, far, page):
+@pytest.mark.parametrize("H,D,V,QR,R,page", [(16, 32, 16, 48, 128, 16), (12, 16, 24, 32, 64, 32), (3, 64, 64, 96, 64, 16), (40, 8, 8, 16, 64, 64),
+                                             (16, 16, 8, 24, 128, 8)])
+def test_latent_attention_on_tensor_cores(H, D, V, QR, R, page):
+    """Latents of 64 and 128 in bfloat16: prompt portions of 150, 9 and 60 tokens on the tcgen05 kernel with all heads on the
+    one cached row (16, 12, 3 and 40 heads: tiles of 8, 10, 42 and 3 tokens), portions of 3 and single tokens on the split-key
+    kernel with the heads in groups of at most 8, each head's own sink in both; pages of 8 leave everything to the latter."""
+    rng = np.random.default_rng(H * D + R)
+    m = {"heads": H, "dim": D, "vdim": V, "q_rank": QR, "kv_rank": R, "scale": 0.4}
+    W = _latent_weights(rng, m, "bfloat16")
+    T = 150 + 9 + 3 + 60 + 20
+    proj = rng.standard_normal((T, QR + R + H * V)) * 2.0
+    want = _plain_latent_from_rows(m, 1e-5, proj, W)
+    got = _latent_by_kernels("bfloat16", m, 1e-5, proj, W, [150, 9, 3, 60] + [1] * 20, page, tensor_cores=True)
+    assert np.abs(got - want).max() <= 3e-2 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype,R,tensor_cores", [("float32", 16, False), ("bfloat16", 16, False), ("bfloat16", 64, True), ("bfloat16", 128, True)])
+@pytest.mark.parametrize("far,page", [(0, 16), (15, 16), (16, 16), (3, 4), (31, 8), (127, 32), (128, 64)])
+def test_a_far_latent_among_hundreds_and_the_sink(dtype, R, tensor_cores, far, page):
     """One latent, before, at or after a page border, outweighs the hundreds of others for the queries that look for it,
-    in a prompt of 600 and in 20 single tokens; one head's sink takes exactly half of the weight from it, and the other
-    head's sink mutes a query that finds nothing (tests/keralix_cases.py: far_latent_case)."""
-    m, W, proj, seekers, blind, v_far, want = C.far_latent_case(far, seed=far * 31 + page, T=620, prompt=600)
+    in a prompt of 600 and in 20 single tokens; the odd heads' sink takes exactly half of the weight from it, and the even
+    heads' sink mutes a query that finds nothing (tests/keralix_cases.py: far_latent_case).  With tensor_cores through
+    the tcgen05 prompt kernel and the split-key kernel (twelve heads: two groups of six)."""
+    H = 12 if tensor_cores else 2
+    m, W, proj, seekers, blind, v_far, want = C.far_latent_case(far, seed=far * 31 + page, T=620, prompt=600, R=R, H=H)
     if dtype == "bfloat16":
         W = dict(W, uv=_bf16_round(W["uv"]))
         want = C.latent_rows_plain(m, 1e-5, proj, W)
-    got = _latent_by_kernels(dtype, m, 1e-5, proj, W, [600] + [1] * 20, page)
+    got = _latent_by_kernels(dtype, m, 1e-5, proj, W, [600] + [1] * 20, page, tensor_cores=tensor_cores)
     tol = (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
     assert np.abs(got - want).max() <= tol
     for t in seekers:
         assert np.abs(got[t, :8] - v_far[0]).max() < 0.05 * np.abs(v_far[0]).max()
+        assert np.abs(got[t, 8:16] - 0.5 * v_far[1]).max() < 0.05 * np.abs(v_far[1]).max()
 
 
 def _window_attention_by_kernels(dtype, m, rows, bias, taps_w, cuts, page, tensor_cores=False):
