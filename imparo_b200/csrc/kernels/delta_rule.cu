@@ -5,11 +5,11 @@
 //
 //  (1) delta_prepare: per row, in 32-bit: q and k of every query/key head divided by sqrt(sum of squares + unit_eps)
 //      (q also times q_scale), beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias)) written over a.
-//  (2) delta_scan: the value columns of S are independent of one another, so a lane owns a stretch of DPT key
-//      channels of one column p: LPC lanes share a column (dim <= DPT * LPC), a warp walks a request's rows in order
-//      with its 32 / LPC columns in registers.  The row's q, k and g pass through shared memory (the next row is
-//      fetched while the current one is computed); the two sums over the key channels are finished by shuffles among
-//      the LPC lanes.  The additions' order depends on (dim, LPC) only.
+//  (2) delta_scan: the value columns of S are independent of one another, so a lane owns a stretch of 8 key channels
+//      of one column p: LPC lanes share a column (dim <= 8 * LPC), a warp walks a request's rows in order with its
+//      32 / LPC columns in registers.  The rows' q, k, g, v and beta pass through shared memory in blocks of four rows,
+//      copied asynchronously two blocks ahead; the two sums over the key channels are finished by shuffles among the
+//      LPC lanes, the read-out's off the recurrence's chain.  The additions' order depends on (dim, LPC) only.
 //  (3) head_norm_gate: every head's output divided by its root mean square over vdim, times a weight [vdim] shared
 //      by the heads, times sigmoid(gate).
 #include "common.cuh"
@@ -48,29 +48,51 @@ delta_prepare_kernel(float* __restrict__ qkv, size_t qkv_stride, int q_off, int 
 
 // ---- (2) ------------------------------------------------------------------------------------------------------
 constexpr int DR_WARPS = 4;
+constexpr int DR_RB = 4;        // rows per staged block
+constexpr int DR_ST = 3;        // blocks in flight or in use per warp
+constexpr int DR_DPT = 8;       // key channels of a column that one lane keeps
 
-template <int DPT, int LPC>
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void dr_wait2() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
+
+__host__ __device__ constexpr int dr_row_floats(int dp, int cpw) { return (3 * dp + cpw + 1 + 3) & ~3; }      // q | k | g | v of the warp's columns | beta
+
+// LPC lanes share a value column (dim <= 8 * LPC); a warp has 32 / LPC columns.  The rows' q, k, g, v and beta come
+// through shared memory in blocks of DR_RB rows, asynchronously, two blocks ahead of the one in use, so that the walk
+// over a request's rows never waits for the memory's latency.  VEC: 16-byte copies (dim, offsets and strides multiples of
+// four floats, 16-byte aligned bases); else 4-byte copies.  The additions' order depends on (dim, LPC) only.
+template <int LPC, bool VEC>
 __global__ void __launch_bounds__(DR_WARPS * 32)
 delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, int k_off, int v_off,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ state,
                   const int* __restrict__ item_row_start, const int* __restrict__ item_slot, int n_slots,
                   float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int* status) {
+    constexpr int DPT = DR_DPT;
     constexpr int DP = DPT * LPC;                   // padded key size
     constexpr int CPW = 32 / LPC;                   // columns per warp
-    __shared__ __align__(16) float buf[DR_WARPS][2][3 * DP];
+    constexpr int ROWF = dr_row_floats(DP, CPW);
+    extern __shared__ __align__(16) float dr_smem[];
     pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int item = blockIdx.z, h = blockIdx.y;
-    const int col = (blockIdx.x * DR_WARPS + warp) * CPW + lane / LPC;
+    const int col0 = (blockIdx.x * DR_WARPS + warp) * CPW;
+    const int col = col0 + lane / LPC;
     const int part = lane % LPC;
     const int first = item_row_start[item], n = item_row_start[item + 1] - first;
     const int slot = item_slot[item];
     pdl_wait();
-    if ((blockIdx.x * DR_WARPS + warp) * CPW >= vdim) return;            // a warp without columns
+    if (col0 >= vdim) return;                                            // a warp without columns
     if (slot < 0 || slot >= n_slots) {
         if (lane == 0 && blockIdx.x == 0 && warp == 0) report(status, IMPARO_ST_SLOT_RANGE, 73, item, slot);
         return;
     }
+    float* stage = dr_smem + (size_t)warp * DR_ST * DR_RB * ROWF;
     const bool live = col < vdim;
     const int kvh = h / (heads / kv_heads);
     float* Sg = state + (((size_t)slot * heads + h) * dim) * vdim;
@@ -80,73 +102,102 @@ delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, i
         const int d = part * DPT + i;
         S[i] = (live && d < dim) ? Sg[(size_t)d * vdim + col] : 0.f;
     }
-    // a row's q, k and g of this head: 3 * DP floats, fetched by the warp's lanes a row ahead
-    constexpr int PER = (3 * DP + 31) / 32;
-    float ahead[PER];
-    auto fetch = [&](int t) {
-        const float* row = qkv + (size_t)t * qkv_stride;
-        const float* gr = g + ((size_t)t * heads + h) * dim;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = lane + 32 * i;
-            const int which = e / DP, d = e % DP;
-            float v = 0.f;
-            if (e < 3 * DP && d < dim)
-                v = which == 0 ? row[q_off + kvh * dim + d] : (which == 1 ? row[k_off + kvh * dim + d] : gr[d]);
-            ahead[i] = v;
+    const int n_blocks = (n + DR_RB - 1) / DR_RB;
+    auto issue = [&](int b) {
+        if (b < n_blocks) {
+            float* dst = stage + (b % DR_ST) * DR_RB * ROWF;
+            const int t0 = first + b * DR_RB, nb = min(DR_RB, n - b * DR_RB);
+            if (VEC) {
+                constexpr int VPS = DP / 4, VPR = 3 * VPS;                // 16-byte groups per stretch and per row
+                for (int e = lane; e < nb * VPR; e += 32) {
+                    const int r = e / VPR, c = e % VPR;
+                    const int which = c / VPS, d = (c % VPS) * 4;
+                    float* to = dst + r * ROWF + which * DP + d;
+                    if (d < dim) {                                       // dim is a multiple of 4: a group is whole or absent
+                        const float* src = which == 2 ? g + ((size_t)(t0 + r) * heads + h) * dim + d
+                                                      : qkv + (size_t)(t0 + r) * qkv_stride + (which == 0 ? q_off : k_off) + kvh * dim + d;
+                        dr_cp16(to, src);
+                    } else {
+                        *reinterpret_cast<float4*>(to) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            } else {
+                for (int e = lane; e < nb * 3 * DP; e += 32) {
+                    const int r = e / (3 * DP), c = e % (3 * DP);
+                    const int which = c / DP, d = c % DP;
+                    float* to = dst + r * ROWF + c;
+                    if (d < dim) {
+                        const float* src = which == 2 ? g + ((size_t)(t0 + r) * heads + h) * dim + d
+                                                      : qkv + (size_t)(t0 + r) * qkv_stride + (which == 0 ? q_off : k_off) + kvh * dim + d;
+                        dr_cp4(to, src);
+                    } else {
+                        *to = 0.f;
+                    }
+                }
+            }
+            for (int e = lane; e < nb * (CPW + 1); e += 32) {            // the values of this warp's columns, and beta
+                const int r = e / (CPW + 1), c = e % (CPW + 1);
+                float* to = dst + r * ROWF + 3 * DP + c;
+                if (c == CPW) dr_cp4(to, beta + (size_t)(t0 + r) * heads + h);
+                else if (col0 + c < vdim) dr_cp4(to, qkv + (size_t)(t0 + r) * qkv_stride + v_off + h * vdim + col0 + c);
+                else *to = 0.f;
+            }
         }
+        dr_commit();                                                     // (an empty group keeps the count in step)
     };
-    auto stash = [&](int b) {
+    issue(0);
+    issue(1);
+    for (int b = 0; b < n_blocks; ++b) {
+        issue(b + 2);                                                    // into the stage that block b - 1 has left
+        dr_wait2();                                                      // this lane's copies of block b are done
+        __syncwarp();                                                    // ... and every other lane's
+        const float* src = stage + (b % DR_ST) * DR_RB * ROWF;
+        const int nb = min(DR_RB, n - b * DR_RB);
+        float o_part[DR_RB];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = lane + 32 * i;
-            if (e < 3 * DP) buf[warp][b][e] = ahead[i];
+        for (int r = 0; r < DR_RB; ++r) {
+            o_part[r] = 0.f;
+            if (r < nb) {
+                const float* row = src + r * ROWF;
+                const float* qs = row + part * DPT;
+                const float* ks = qs + DP;
+                const float* gs = ks + DP;
+                const float vv = row[3 * DP + lane / LPC], bb = row[3 * DP + CPW];
+                float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(gs + i);
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+                    S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
+                    r0 += S[i] * k4.x; r1 += S[i + 1] * k4.y; r2 += S[i + 2] * k4.z; r3 += S[i + 3] * k4.w;
+                }
+                float rs = (r0 + r1) + (r2 + r3);
+#pragma unroll
+                for (int o = LPC / 2; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+                const float u = bb * (vv - rs);
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
+                    S[i] += k4.x * u; S[i + 1] += k4.y * u; S[i + 2] += k4.z * u; S[i + 3] += k4.w * u;
+                    o0 += S[i] * q4.x; o1 += S[i + 1] * q4.y; o2 += S[i + 2] * q4.z; o3 += S[i + 3] * q4.w;
+                }
+                o_part[r] = (o0 + o1) + (o2 + o3);
+            }
         }
-    };
-    if (n > 0) { fetch(first); stash(0); }
-    __syncwarp();
-    float v_next = 0.f, b_next = 0.f;
-    if (n > 0) {
-        v_next = live ? qkv[(size_t)first * qkv_stride + v_off + h * vdim + col] : 0.f;
-        b_next = beta[(size_t)first * heads + h];
-    }
-    for (int j = 0; j < n; ++j) {
-        const int t = first + j;
-        const float vv = v_next, bb = b_next;
-        if (j + 1 < n) {
-            fetch(t + 1);
-            v_next = live ? qkv[(size_t)(t + 1) * qkv_stride + v_off + h * vdim + col] : 0.f;
-            b_next = beta[(size_t)(t + 1) * heads + h];
+        // the read-outs' sums over the lanes of a column: off the recurrence's chain, the block's rows side by side
+#pragma unroll
+        for (int s2 = LPC / 2; s2 > 0; s2 >>= 1) {
+#pragma unroll
+            for (int r = 0; r < DR_RB; ++r) o_part[r] += __shfl_xor_sync(0xffffffffu, o_part[r], s2);
         }
-        const float* qs = buf[warp][j & 1] + part * DPT;
-        const float* ks = qs + DP;
-        const float* gs = ks + DP;
-        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+        if (live && part == 0) {
 #pragma unroll
-        for (int i = 0; i < DPT; i += 4) {
-            const float4 g4 = *reinterpret_cast<const float4*>(gs + i);
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-            S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
-            r0 += S[i] * k4.x; r1 += S[i + 1] * k4.y; r2 += S[i + 2] * k4.z; r3 += S[i + 3] * k4.w;
+            for (int r = 0; r < DR_RB; ++r)
+                if (r < nb) out[((size_t)(first + b * DR_RB + r) * heads + h) * vdim + col] = o_part[r];
         }
-        float r = (r0 + r1) + (r2 + r3);
-#pragma unroll
-        for (int o = LPC / 2; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-        const float u = bb * (vv - r);
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-        for (int i = 0; i < DPT; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
-            S[i] += k4.x * u; S[i + 1] += k4.y * u; S[i + 2] += k4.z * u; S[i + 3] += k4.w * u;
-            o0 += S[i] * q4.x; o1 += S[i + 1] * q4.y; o2 += S[i + 2] * q4.z; o3 += S[i + 3] * q4.w;
-        }
-        float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-        for (int s = LPC / 2; s > 0; s >>= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
-        if (live && part == 0) out[((size_t)t * heads + h) * vdim + col] = o;
-        if (j + 1 < n) stash((j + 1) & 1);
-        __syncwarp();
+        __syncwarp();                                                    // the stage may be written again
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -201,17 +252,30 @@ extern "C" int imparo_delta_scan(const float* qkv, long long qkv_stride, int q_o
                                  cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || dim > 256 || vdim < 1) return -2;
-#define IMPARO_DS(DPT_, LPC_) do { \
-        const int cpw = 32 / (LPC_); \
+    const bool vec = dim % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && qkv_stride % 4 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)g) & 15) == 0;
+    cudaError_t e = cudaSuccess;
+#define IMPARO_DS(LPC_, VEC_) do { \
+        constexpr int cpw = 32 / (LPC_); \
+        constexpr size_t smem = (size_t)DR_WARPS * DR_ST * DR_RB * dr_row_floats(DR_DPT * (LPC_), cpw) * sizeof(float); \
+        static bool configured = false; \
+        if (!configured) { \
+            e = cudaFuncSetAttribute(delta_scan_kernel<LPC_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+            configured = true; \
+        } \
         const int warps = (vdim + cpw - 1) / cpw; \
-        launch(delta_scan_kernel<DPT_, LPC_>, dim3((warps + DR_WARPS - 1) / DR_WARPS, heads, n_items), dim3(DR_WARPS * 32), 0, stream, \
+        launch(delta_scan_kernel<LPC_, VEC_>, dim3((warps + DR_WARPS - 1) / DR_WARPS, heads, n_items), dim3(DR_WARPS * 32), smem, stream, \
                qkv, (size_t)qkv_stride, q_off, k_off, v_off, g, beta, state, item_row_start, item_slot, n_slots, out, heads, \
                kv_heads, dim, vdim, status); } while (0)
-    if (dim <= 16) IMPARO_DS(16, 1);
-    else if (dim <= 32) IMPARO_DS(32, 1);
-    else if (dim <= 64) IMPARO_DS(32, 2);
-    else if (dim <= 128) IMPARO_DS(32, 4);
-    else IMPARO_DS(32, 8);
+#define IMPARO_DS2(LPC_) do { if (vec) IMPARO_DS(LPC_, true); else IMPARO_DS(LPC_, false); } while (0)
+    if (dim <= 8) IMPARO_DS2(1);
+    else if (dim <= 16) IMPARO_DS2(2);
+    else if (dim <= 32) IMPARO_DS2(4);
+    else if (dim <= 64) IMPARO_DS2(8);
+    else if (dim <= 128) IMPARO_DS2(16);
+    else IMPARO_DS2(32);
+#undef IMPARO_DS2
 #undef IMPARO_DS
     IMPARO_CHECK_LAUNCH();
     return 0;
