@@ -13,6 +13,7 @@
 //  (3) head_norm_gate: every head's output divided by its root mean square over vdim, times a weight [vdim] shared
 //      by the heads, times sigmoid(gate).
 #include "common.cuh"
+#include <type_traits>
 
 namespace imparo {
 
@@ -103,7 +104,59 @@ delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, i
         S[i] = (live && d < dim) ? Sg[(size_t)d * vdim + col] : 0.f;
     }
     const int n_blocks = (n + DR_RB - 1) / DR_RB;
+    // FAST (16-byte copies and dim > 32): a lane copies the same pieces of every block, so where they come from and go
+    // to is worked out once: ITEMS 16-byte groups of q | k | g (an offset from the block's first row, the row and the place
+    // in the stage packed into one word) and at most one value or beta.  Stretches beyond dim stay zero from the start.
+    constexpr bool FAST = VEC && LPC >= 8;
+    constexpr int ITEMS = FAST ? (DR_RB * 3 * DP / 4) / 32 : 1;
+    int f_off[ITEMS], f_key[ITEMS];                  // key: place in the stage | row << 24 | from g << 28 | absent << 29
+    const float* vb_ptr = nullptr;
+    size_t vb_step = 0;
+    int vb_key = -1;
+    if (FAST) {
+        constexpr int VPS = DP / 4, VPR = 3 * VPS;
+        for (int e = lane; e < DR_ST * DR_RB * ROWF; e += 32) stage[e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int e = lane + 32 * i;
+            const int r = e / VPR, c = e % VPR;
+            const int which = c / VPS, d = (c % VPS) * 4;
+            f_off[i] = which == 2 ? (r * heads + h) * dim + d : r * (int)qkv_stride + (which == 0 ? q_off : k_off) + kvh * dim + d;
+            f_key[i] = (r * ROWF + which * DP + d) | (r << 24) | ((which == 2) << 28) | ((d >= dim) << 29);
+        }
+        if (lane < DR_RB * (CPW + 1)) {
+            const int r = lane / (CPW + 1), c = lane % (CPW + 1);
+            if (c == CPW) {
+                vb_ptr = beta + (size_t)(first + r) * heads + h;
+                vb_step = (size_t)DR_RB * heads;
+                vb_key = (r * ROWF + 3 * DP + c) | (r << 24);
+            } else if (col0 + c < vdim) {
+                vb_ptr = qkv + (size_t)(first + r) * qkv_stride + v_off + h * vdim + col0 + c;
+                vb_step = (size_t)DR_RB * qkv_stride;
+                vb_key = (r * ROWF + 3 * DP + c) | (r << 24);
+            }
+        }
+        __syncwarp();
+    }
     auto issue = [&](int b) {
+        if (FAST) {
+            if (b < n_blocks) {
+                float* dst = stage + (b % DR_ST) * DR_RB * ROWF;
+                const int nb = min(DR_RB, n - b * DR_RB);
+                const float* base_q = qkv + (size_t)(first + b * DR_RB) * qkv_stride;
+                const float* base_g = g + (size_t)(first + b * DR_RB) * heads * dim;
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) {
+                    const int key = f_key[i];
+                    if (((key >> 24) & 15) < nb && !(key & (1 << 29)))
+                        dr_cp16(dst + (key & 0xffffff), ((key >> 28) & 1 ? base_g : base_q) + f_off[i]);
+                }
+                if (vb_key >= 0 && (vb_key >> 24) < nb) dr_cp4(dst + (vb_key & 0xffffff), vb_ptr);
+                vb_ptr += vb_step;
+            }
+            dr_commit();
+            return;
+        }
         if (b < n_blocks) {
             float* dst = stage + (b % DR_ST) * DR_RB * ROWF;
             const int t0 = first + b * DR_RB, nb = min(DR_RB, n - b * DR_RB);
@@ -154,10 +207,11 @@ delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, i
         const float* src = stage + (b % DR_ST) * DR_RB * ROWF;
         const int nb = min(DR_RB, n - b * DR_RB);
         float o_part[DR_RB];
+        auto rows = [&](auto whole) {                                    // whole: the block has all its rows, nothing to test
 #pragma unroll
         for (int r = 0; r < DR_RB; ++r) {
             o_part[r] = 0.f;
-            if (r < nb) {
+            if (decltype(whole)::value || r < nb) {
                 const float* row = src + r * ROWF;
                 const float* qs = row + part * DPT;
                 const float* ks = qs + DP;
@@ -186,6 +240,8 @@ delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, i
                 o_part[r] = (o0 + o1) + (o2 + o3);
             }
         }
+        };
+        if (nb == DR_RB) rows(std::true_type{}); else rows(std::false_type{});
         // the read-outs' sums over the lanes of a column: off the recurrence's chain, the block's rows side by side
 #pragma unroll
         for (int s2 = LPC / 2; s2 > 0; s2 >>= 1) {
