@@ -748,10 +748,10 @@ def main():
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
     ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar", "keralix"],
-                    help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
+                    help="headline (default): the one JSON line described at the top of this file.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit.  "
-                         "vipotar: the Vipotar design at two sizes beside LFM2 at equal sizes")
+                         "vipotar / negotar: that design at two sizes beside LFM2 at equal sizes.  keralix: the Keralix design at two sizes beside Vipotar")
     ap.add_argument("--requests", type=int, default=32, help="continuous: requests in all (the baseline's workload has 32)")
     ap.add_argument("--long-check-layers", type=int, default=4, help="long: layers of the 32-bit check against the plain implementation")
     args = ap.parse_args()
