@@ -28,7 +28,7 @@ def far_latent_case(far, seed, T=620, prompt=600, R=16, H=2):
     m = {"heads": H, "dim": D, "vdim": V, "q_rank": QR, "kv_rank": R, "scale": 8.0 / R}
     W = {"uq": np.concatenate([np.eye(D, QR)] * H), "uk": np.concatenate([np.eye(D, R)] * H) * 1.5,
          "uv": rng.standard_normal((H * V, R)) / np.sqrt(R), "dq.norm": np.ones(QR), "dkv.norm": np.ones(R),
-         "sink": np.array([8.0, 12.0] * (H // 2))}
+         "sink": np.array(([8.0, 12.0] * H)[:H])}
     direction = rng.standard_normal(R)
     direction /= np.sqrt(np.mean(direction ** 2))                       # rms 1: the norms leave it as it is
     proj = rng.standard_normal((T, QR + R + H * V))

@@ -486,6 +486,21 @@ def test_a_far_latent_among_hundreds_and_the_sink(dtype, R, tensor_cores, far, p
         assert np.abs(got[t, 8:16] - 0.5 * v_far[1]).max() < 0.05 * np.abs(v_far[1]).max()
 
 
+@pytest.mark.parametrize("R,H", [(64, 12), (64, 3), (128, 16)])
+def test_sinks_where_a_tile_pair_shares_a_block(R, H):
+    """A block table of 1,024 positions or more sends latents of 64 to the tcgen05 kernel that gives a CTA two query tiles
+    in turn (latents of 128 stay on the one-tile kernel): the far latent among 1,080 and both kinds of sink once more."""
+    m, W, proj, seekers, blind, v_far, want = C.far_latent_case(15, seed=R + H, T=1100, prompt=1080, R=R, H=H)
+    W = dict(W, uv=_bf16_round(W["uv"]))
+    want = C.latent_rows_plain(m, 1e-5, proj, W)
+    got = _latent_by_kernels("bfloat16", m, 1e-5, proj, W, [1080] + [1] * 20, 16, tensor_cores=True)
+    assert np.abs(got - want).max() <= 3e-2 * np.abs(want).max()
+    for t in seekers:
+        assert np.abs(got[t, :8] - v_far[0]).max() < 0.05 * np.abs(v_far[0]).max()
+        if H > 1:
+            assert np.abs(got[t, 8:16] - 0.5 * v_far[1]).max() < 0.05 * np.abs(v_far[1]).max()
+
+
 def _window_attention_by_kernels(dtype, m, rows, bias, taps_w, cuts, page, tensor_cores=False):
     """The convolution, the head preparation with keys as values, and the attention on one request cut as `cuts`;
     rows: the 32-bit product [T, q | k] before biases."""
