@@ -458,7 +458,7 @@ def workload_keralix(args):
                                lat_vdim=64, q_rank=384, kv_rank=128, delta_heads=8, delta_kv_heads=4, delta_dim=64, delta_vdim=128,
                                inner=64, ff=4096, vocab=32768),
              "width2048": dict(width=2048, layers=8, streams=4, heads=32, kv_heads=8, head=64, window=1024, lat_heads=32, lat_dim=64,
-                               lat_vdim=64, q_rank=768, kv_rank=256, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
+                               lat_vdim=64, q_rank=768, kv_rank=128, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
                                inner=128, ff=8192, vocab=65536)}
     out = {"metric": "Keralix beside Vipotar at equal sizes: prefill of one prompt, decode at batch 8 with 2,048 positions",
            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "sizes": {}}

@@ -45,7 +45,9 @@ __global__ void streams_norm_kernel(const float* __restrict__ x, const int* __re
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(u_s[i] * scale * w[i]);
 }
 
-template <typename TOut>
+// V: columns per thread and access (4: 16-byte loads and stores, for widths that are multiples of four; 1: any width).
+// Every element's sums run in the same order either way.
+template <typename TOut, int V>
 __global__ void streams_mix_add_kernel(float* __restrict__ x, int n, const float* __restrict__ mix,
                                        const float* __restrict__ b, const float* __restrict__ y,
                                        const float* __restrict__ na, const float* __restrict__ nw, float neps,
@@ -62,25 +64,47 @@ __global__ void streams_mix_add_kernel(float* __restrict__ x, int n, const float
     float* xr = x + (size_t)r * n * width;
     const float* yr = y + (size_t)r * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float old[HC_MAX];
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        float old[HC_MAX][V], yv[V], u[V];
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s) old[s] = s < n ? xr[(size_t)s * width + i] : 0.f;
-        const float yv = yr[i];
-        float u = 0.f;
+        for (int s = 0; s < HC_MAX; ++s) {
+            if (V == 4) {
+                const float4 q = s < n ? *reinterpret_cast<const float4*>(xr + (size_t)s * width + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                old[s][0] = q.x; old[s][1 % V] = q.y; old[s][2 % V] = q.z; old[s][3 % V] = q.w;
+            } else {
+                old[s][0] = s < n ? xr[(size_t)s * width + i] : 0.f;
+            }
+        }
+        if (V == 4) {
+            const float4 q = *reinterpret_cast<const float4*>(yr + i);
+            yv[0] = q.x; yv[1 % V] = q.y; yv[2 % V] = q.z; yv[3 % V] = q.w;
+        } else {
+            yv[0] = yr[i];
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) u[e] = 0.f;
 #pragma unroll
         for (int t = 0; t < HC_MAX; ++t) {
             if (t < n) {
-                float v = m_s[t] * old[0];                              // mix[s, t] at s * n + t
+                float v[V];
 #pragma unroll
-                for (int s = 1; s < HC_MAX; ++s)
-                    if (s < n) v += m_s[s * n + t] * old[s];
-                v += b_s[t] * yv;
-                xr[(size_t)t * width + i] = v;
-                u = t == 0 ? a_s[0] * v : u + a_s[t] * v;
+                for (int e = 0; e < V; ++e) {
+                    float acc = m_s[t] * old[0][e];                     // mix[s, t] at s * n + t
+#pragma unroll
+                    for (int s = 1; s < HC_MAX; ++s)
+                        if (s < n) acc += m_s[s * n + t] * old[s][e];
+                    acc += b_s[t] * yv[e];
+                    v[e] = acc;
+                    u[e] = t == 0 ? a_s[0] * acc : u[e] + a_s[t] * acc;
+                }
+                if (V == 4) *reinterpret_cast<float4*>(xr + (size_t)t * width + i) = make_float4(v[0], v[1 % V], v[2 % V], v[3 % V]);
+                else xr[(size_t)t * width + i] = v[0];
             }
         }
-        if (nw) { u_s[i] = u; ss += u * u; }
+        if (nw) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) { u_s[i + e] = u[e]; ss += u[e] * u[e]; }
+        }
     }
     if (!nw) return;
     ss = block_sum(ss, scratch);
@@ -142,15 +166,17 @@ extern "C" int imparo_streams_mix_add(float* x, int n, const float* mix, const f
     if (n < 1 || n > HC_MAX) return -2;
     if ((size_t)width * sizeof(float) > 96 * 1024) return -3;
     const size_t smem = nw ? (size_t)width * sizeof(float) : 0;
+    const bool vec = width % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+#define IMPARO_MIX(T_, V_) do { \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_mix_add_kernel<T_, V_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch(streams_mix_add_kernel<T_, V_>, dim3(n_rows), dim3(hc_threads(width / (V_))), smem, stream, x, n, mix, b, y, na, nw, neps, \
+               (T_*)nout, width); } while (0)
     if (!nw || out_dtype == IMPARO_DT_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_mix_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch(streams_mix_add_kernel<float>, dim3(n_rows), dim3(hc_threads(width)), smem, stream, x, n, mix, b, y, na, nw, neps,
-               (float*)nout, width);
+        if (vec) IMPARO_MIX(float, 4); else IMPARO_MIX(float, 1);
     } else if (out_dtype == IMPARO_DT_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_mix_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch(streams_mix_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(hc_threads(width)), smem, stream, x, n, mix, b, y, na, nw, neps,
-               (__nv_bfloat16*)nout, width);
+        if (vec) IMPARO_MIX(__nv_bfloat16, 4); else IMPARO_MIX(__nv_bfloat16, 1);
     } else return -1;
+#undef IMPARO_MIX
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -7,8 +7,8 @@
 //  (1) latent_norm_store: per row of a 32-bit product [.. q latent .. | .. kv latent ..], each stretch divided by its
 //      root mean square times a weight; the query latent goes to an activation tensor, the kv latent into its page.
 //  (2) heads_linear: out[t, h, :] = W[h] x[t, h, :] for every head h (W [heads, out, in]), optionally times
-//      sigmoid(gate[t, h, :]) (a 32-bit product's columns).  A block takes a tile of rows of one head; the head's
-//      matrix is read once per tile.  32-bit sums, in order over `in`.
+//      sigmoid(gate[t, h, :]) (a 32-bit product's columns).  A warp per output feature of a head and tile of eight rows;
+//      32-bit sums (for steps of few rows: many rows go to the library's batched product).
 #include "common.cuh"
 
 namespace imparo {
@@ -53,39 +53,38 @@ latent_norm_store_kernel(const float* __restrict__ proj, size_t stride, int q_of
 
 constexpr int HL_ROWS = 8;
 
+// A warp per (head, output feature) and tile of HL_ROWS rows: the lanes stride over the head's inputs (the matrix row is
+// read once, coalesced), every row's sum is finished by a warp sum in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(128)
 heads_linear_kernel(const T* __restrict__ x, size_t x_stride, const T* __restrict__ w, const float* __restrict__ gate,
                     size_t gate_stride, T* __restrict__ out, size_t out_stride, int n_tok, int n_in, int n_out) {
-    extern __shared__ float xs[];                       // [HL_ROWS, n_in]
     pdl_trigger();
     pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y;
-    const int t0 = blockIdx.x * HL_ROWS;
+    const int o = blockIdx.x * 4 + warp;
+    const int t0 = blockIdx.z * HL_ROWS;
+    if (o >= n_out) return;
     const int rows = min(HL_ROWS, n_tok - t0);
-    for (int e = threadIdx.x; e < HL_ROWS * n_in; e += blockDim.x) {
-        const int r = e / n_in, i = e % n_in;
-        xs[e] = r < rows ? to_f32(x[(size_t)(t0 + r) * x_stride + (size_t)h * n_in + i]) : 0.f;
+    const T* wr = w + ((size_t)h * n_out + o) * n_in;
+    const T* xh = x + (size_t)t0 * x_stride + (size_t)h * n_in;
+    float acc[HL_ROWS];
+#pragma unroll
+    for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
+    for (int i = lane; i < n_in; i += 32) {
+        const float wv = to_f32(wr[i]);
+#pragma unroll
+        for (int r = 0; r < HL_ROWS; ++r)
+            if (r < rows) acc[r] += wv * to_f32(xh[(size_t)r * x_stride + i]);
     }
-    __syncthreads();
-    const T* wh = w + (size_t)h * n_out * n_in;
-    for (int o = threadIdx.x; o < n_out; o += blockDim.x) {
-        float acc[HL_ROWS];
 #pragma unroll
-        for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
-        const T* wr = wh + (size_t)o * n_in;
-        for (int i = 0; i < n_in; ++i) {
-            const float wv = to_f32(wr[i]);
-#pragma unroll
-            for (int r = 0; r < HL_ROWS; ++r) acc[r] += wv * xs[r * n_in + i];
-        }
-#pragma unroll
-        for (int r = 0; r < HL_ROWS; ++r) {
-            if (r < rows) {
-                float v = acc[r];
-                if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)(t0 + r) * gate_stride + (size_t)h * n_out + o]));
-                out[(size_t)(t0 + r) * out_stride + (size_t)h * n_out + o] = from_f32<T>(v);
-            }
+    for (int r = 0; r < HL_ROWS; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < rows) {
+            float res = v;
+            if (gate) res *= 1.0f / (1.0f + expf(-gate[(size_t)(t0 + r) * gate_stride + (size_t)h * n_out + o]));
+            out[(size_t)(t0 + r) * out_stride + (size_t)h * n_out + o] = from_f32<T>(res);
         }
     }
 }
@@ -148,9 +147,10 @@ extern "C" int imparo_heads_linear(const void* x, long long x_stride, const void
                                    cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (heads < 1 || n_in < 1 || n_out < 1) return -2;
-    const size_t smem = (size_t)HL_ROWS * n_in * sizeof(float);
-    if (smem > 48 * 1024) return -3;
-    const dim3 grid((n_tok + HL_ROWS - 1) / HL_ROWS, heads);
+    const size_t smem = 0;
+    const int tiles = (n_tok + HL_ROWS - 1) / HL_ROWS;
+    if (tiles > 65535 || heads > 65535) return -2;
+    const dim3 grid((n_out + 3) / 4, heads, tiles);
     if (dtype == IMPARO_DT_F32)
         launch(heads_linear_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, (size_t)x_stride, (const float*)w, gate,
                (size_t)gate_stride, (float*)out, (size_t)out_stride, n_tok, n_in, n_out);
