@@ -553,7 +553,7 @@ _plain_window_from_rows = C.window_rows_plain
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,hd,taps,rot,cap,window", [
     (4, 2, 16, 3, {"dims": 8, "base": 300.0}, 5.0, 9), (6, 1, 24, 1, None, None, None), (3, 3, 32, 2, {"dims": 32, "base": 500.0}, 25.0, 70),
-    (8, 1, 80, 4, {"dims": 48, "base": 250000.0}, 2.0, 4), (2, 1, 40, 5, {"dims": 6, "base": 20.0}, None, 1)])
+    (8, 1, 80, 4, {"dims": 48, "base": 400000.0}, 2.0, 4), (2, 1, 40, 5, {"dims": 6, "base": 20.0}, None, 1)])
 def test_convolved_keys_as_values_attention_kernels(dtype, nh, nkv, hd, taps, rot, cap, window):
     """Biases, the convolution with its state, rotation, keys as their own values, the cap and the window: a prompt of 45
     tokens, then 30 tokens one by one on the same cache (pages of 4: every border is crossed)."""

@@ -38,7 +38,7 @@ def draw_config(seed, fast=False):
         if rng.random() < 0.8:
             d["softcap"] = float(pick([2.0, 8.0, 25.0, 50.0]))
         if rng.random() < 0.85:
-            d["rot"] = {"dims": 2 * int(rng.integers(1, dim // 2 + 1)), "base": float(pick([50.0, 10000.0, 250000.0]))}
+            d["rot"] = {"dims": 2 * int(rng.integers(1, dim // 2 + 1)), "base": float(pick([50.0, 10000.0, 500000.0]))}
         if rng.random() < 0.85:
             d["mask"] = {"size": int(pick([1, 2, 5, 16, 17, 31, 64, 100, 300]))}
         return {"type": "attention", "mixer": d}
