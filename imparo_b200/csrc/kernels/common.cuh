@@ -90,6 +90,38 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 // approximate instructions (a few units in the last place of 32-bit, far below the rounding that follows).
 __device__ __forceinline__ float silu_bf16(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// What a gated feed-forward makes of a (gate, up) pair of pre-activations:
+//   0  silu(g) * u
+//   1  gelu(g) * u with gelu(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   2  with g' = min(g, limit) and u' = clamp(u, -limit, limit):  g' * sigmoid(1.702 g') * (u' + 1)
+#define IMPARO_GATED_SILU 0
+#define IMPARO_GATED_GELU_TANH 1
+#define IMPARO_GATED_CLAMPED 2
+__device__ __forceinline__ float gated_act(int kind, float limit, float g, float u) {
+    if (kind == IMPARO_GATED_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    if (kind == IMPARO_GATED_GELU_TANH)
+        return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return silu(g) * u;
+}
+// The same for results that are rounded to bfloat16 at once (approximate exponential, division and tanh).
+__device__ __forceinline__ float gated_act_bf16(int kind, float limit, float g, float u) {
+    if (kind == IMPARO_GATED_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    }
+    if (kind == IMPARO_GATED_GELU_TANH) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        return 0.5f * g * (1.0f + t) * u;
+    }
+    return silu_bf16(g) * u;
+}
+
 }  // namespace imparo
 
 // ---- programmatic dependent launch ----------------------------------------------------

@@ -10,8 +10,8 @@
 //      32 / LPC columns in registers.  The rows' q, k, g, v and beta pass through shared memory in blocks of four rows
 //      that the CTA copies asynchronously two blocks ahead; the two sums over the key channels are finished by shuffles
 //      among the LPC lanes, the read-out's off the recurrence's chain.  The additions' order depends on the key size only.
-//  (3) head_norm_gate: every head's output divided by its root mean square over vdim, times a weight [vdim] shared
-//      by the heads, times sigmoid(gate).
+//  (3) head_norm_gate: every head's output divided by its root mean square over vdim, times a weight ([vdim] shared
+//      by the heads, or [heads * vdim] with each head's own), times sigmoid(gate).
 #include "common.cuh"
 #include <type_traits>
 
@@ -269,7 +269,7 @@ delta_scan_kernel(const float* __restrict__ qkv, size_t qkv_stride, int q_off, i
 template <typename TOut>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps, const float* __restrict__ gate,
-                      size_t gate_stride, TOut* __restrict__ out, int heads, int vdim) {
+                      size_t gate_stride, TOut* __restrict__ out, int heads, int vdim, int w_head_stride) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -282,8 +282,9 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
         ss = warp_sum(ss);
         const float scale = 1.0f / sqrtf(ss / (float)vdim + eps);
         TOut* dst = out + ((size_t)t * heads + h) * vdim;
+        const float* wh = w + (size_t)h * w_head_stride;
         for (int p = lane; p < vdim; p += 32)
-            dst[p] = from_f32<TOut>(orow[p] * scale * w[p] * (1.0f / (1.0f + expf(-grow[p]))));
+            dst[p] = from_f32<TOut>(orow[p] * scale * wh[p] * (1.0f / (1.0f + expf(-grow[p]))));
     }
 }
 
@@ -342,16 +343,18 @@ extern "C" int imparo_delta_scan(const float* qkv, long long qkv_stride, int q_o
     return 0;
 }
 
-// o: float32 [n_tok, heads * vdim]; w: float32 [vdim]; gate: float32 rows of gate_stride floats (heads * vdim used).
+// o: float32 [n_tok, heads * vdim]; w: float32 [vdim] (w_head_stride 0) or [heads * vdim] (w_head_stride vdim); gate: float32
+// rows of gate_stride floats (heads * vdim used).
 extern "C" int imparo_head_norm_gate(const float* o, const float* w, float eps, const float* gate, long long gate_stride,
-                                     void* out, int out_dtype, int n_tok, int heads, int vdim, cudaStream_t stream) {
+                                     void* out, int out_dtype, int n_tok, int heads, int vdim, int w_head_stride,
+                                     cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     const dim3 grid(n_tok, (heads + 15) / 16 > 0 ? (heads + 15) / 16 : 1);
     if (out_dtype == IMPARO_DT_F32)
-        launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, o, w, eps, gate, (size_t)gate_stride, (float*)out, heads, vdim);
+        launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, o, w, eps, gate, (size_t)gate_stride, (float*)out, heads, vdim, w_head_stride);
     else if (out_dtype == IMPARO_DT_BF16)
         launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, o, w, eps, gate, (size_t)gate_stride,
-               (__nv_bfloat16*)out, heads, vdim);
+               (__nv_bfloat16*)out, heads, vdim, w_head_stride);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

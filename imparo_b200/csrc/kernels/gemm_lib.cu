@@ -53,10 +53,11 @@ static int bind_stream(cudaStream_t stream) {
     return 0;
 }
 
-// One product per head, all in one call: out[m, h, :] = W[h] x[m, h, :] for h < heads, with x rows of lda elements holding
-// heads * K, W [heads, N, K] and out rows of ldc elements holding heads * N (bfloat16 in and out, 32-bit sums).
+// One product per head, all in one call: out[m, h, :] = W[h] x[m, h, :] for h < heads, with x rows of lda elements in which
+// head h's K inputs start at h * a_head, W [heads, N, K] and out rows of ldc elements in which head h's N outputs start at
+// h * c_head (bfloat16 in and out, 32-bit sums).
 extern "C" int imparo_gemm_bf16_heads(const void* A, const void* W, void* C, int M, int heads, int N, int K, int lda, int ldc,
-                                      cudaStream_t stream) {
+                                      int a_head, int c_head, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || heads <= 0) return 0;
     if (!g_handle) return -1;
     int rc = bind_stream(stream);
@@ -64,8 +65,8 @@ extern "C" int imparo_gemm_bf16_heads(const void* A, const void* W, void* C, int
     const float alpha = 1.f, beta = 0.f;
     // column-major view per head: C_h^T[N,M] = W_h[N,K] * A_h^T[K,M]
     cublasStatus_t s = cublasGemmStridedBatchedEx(g_handle, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha,
-                                                  W, CUDA_R_16BF, K, (long long)N * K, A, CUDA_R_16BF, lda, (long long)K, &beta,
-                                                  C, CUDA_R_16BF, ldc, (long long)N, heads, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+                                                  W, CUDA_R_16BF, K, (long long)N * K, A, CUDA_R_16BF, lda, (long long)a_head, &beta,
+                                                  C, CUDA_R_16BF, ldc, (long long)c_head, heads, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
 #ifdef IMPARO_TIMELINE
     launch(imparo::library_product_done_kernel, dim3(1), dim3(32), 0, stream);

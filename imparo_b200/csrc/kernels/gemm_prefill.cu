@@ -52,6 +52,9 @@ struct Params {
     // before its first look at it, and all three skip the same tiles.  null: one matrix for all tiles.
     const int* tile_group;
     int group_rows;
+    // the gated epilogue's activation (gated_act's kinds; 0: silu(gate) * up) and its limit
+    int act;
+    float limit;
 };
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -252,7 +255,8 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 for (int e = 0; e < 4; ++e) {
                                     const float g0 = __uint_as_float(gr[j + 2 * e]), g1 = __uint_as_float(gr[j + 2 * e + 1]);
                                     const float u0 = __uint_as_float(ur[j + 2 * e]), u1 = __uint_as_float(ur[j + 2 * e + 1]);
-                                    w[e] = pack_bf16(silu_bf16(g0) * u0, silu_bf16(g1) * u1);
+                                    w[e] = p.act == 0 ? pack_bf16(silu_bf16(g0) * u0, silu_bf16(g1) * u1)
+                                                      : pack_bf16(gated_act_bf16(p.act, p.limit, g0, u0), gated_act_bf16(p.act, p.limit, g1, u1));
                                 }
                                 *reinterpret_cast<uint4*>(out + f) = make_uint4(w[0], w[1], w[2], w[3]);
                             }
@@ -406,9 +410,11 @@ extern "C" int imparo_gemm_prefill(const void* x, int ldx, int x_rows_alloc, con
 // The same product for rows that are sorted by group: x [rows, K] holds every group's rows from a multiple of 128 on
 // (rows = 128 * m_tiles, padding rows hold anything), w the groups' matrices stacked ([n_groups * N, K]; SwiGLU:
 // [n_groups * 2N, K], each group its gate rows then its up rows), tile_group int32 [m_tiles] on the device (-1: a tile
-// without rows).  epilogue: 0 store bfloat16, 1 store float32, 3 SwiGLU.  Refusals as above.
+// without rows).  epilogue: 0 store bfloat16, 1 store float32, 3 gated (act, limit: gated_act's kinds; 0 is SwiGLU).  Refusals
+// as above.
 extern "C" int imparo_gemm_prefill_grouped(const void* x, int ldx, const void* w, int n_groups, void* out, int ldo, int m_tiles,
-                                           int N, int K, int epilogue, const int* tile_group, int* status, cudaStream_t stream) {
+                                           int N, int K, int epilogue, int act, float limit, const int* tile_group, int* status,
+                                           cudaStream_t stream) {
     if (m_tiles <= 0 || N <= 0 || n_groups <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return -23;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return -23;
@@ -429,6 +435,7 @@ extern "C" int imparo_gemm_prefill_grouped(const void* x, int ldx, const void* w
     p.n_tiles = epilogue == SWIGLU_BF16 ? (N + 127) / 128 : (N + TN - 1) / TN;
     p.tile_group = tile_group;
     p.group_rows = group_rows;
+    p.act = act; p.limit = limit;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles > (1 << 30)) return -2;
     const int ctas = (int)(tiles < sm_count() ? tiles : sm_count());

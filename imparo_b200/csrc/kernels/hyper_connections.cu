@@ -9,7 +9,8 @@
 //      last norm reads it); rows picks input rows.
 //  (2) streams_mix_add: a block per row; with the next sublayer's (a', w', eps') it also leaves that sublayer's
 //      input, so the stream is read and written once between two sublayers.
-//  (3) embed_copies: the embedding row times a factor, written into all n copies.
+//  (3) embed_copies: the embedding row times a factor, plus (optionally) a learned vector of the token's position that
+//      is not scaled, written into all n copies.
 // Everything is 32-bit; sums over s run in the order s = 0, 1, ...; a row's result depends on that row alone.
 #include "common.cuh"
 
@@ -115,6 +116,7 @@ __global__ void streams_mix_add_kernel(float* __restrict__ x, int n, const float
 
 template <typename T>
 __global__ void embed_copies_kernel(const T* __restrict__ table, const int* __restrict__ ids, float scale, int copies,
+                                    const T* __restrict__ pos_table, const int* __restrict__ positions, int n_positions,
                                     float* __restrict__ out, int width, int vocab, int* status) {
     pdl_trigger();
     pdl_wait();
@@ -125,9 +127,19 @@ __global__ void embed_copies_kernel(const T* __restrict__ table, const int* __re
         id = 0;
     }
     const T* row = table + (size_t)id * width;
+    const T* prow = nullptr;
+    if (pos_table) {
+        int p = positions[t];
+        if (p < 0 || p >= n_positions) {
+            if (threadIdx.x == 0) report(status, IMPARO_ST_TOKEN_RANGE, 72, t, p);
+            p = 0;
+        }
+        prow = pos_table + (size_t)p * width;
+    }
     float* o = out + (size_t)t * copies * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = to_f32(row[i]) * scale;
+        float v = to_f32(row[i]) * scale;
+        if (prow) v += to_f32(prow[i]);
         for (int s = 0; s < copies; ++s) o[(size_t)s * width + i] = v;
     }
 }
@@ -181,16 +193,19 @@ extern "C" int imparo_streams_mix_add(float* x, int n, const float* mix, const f
     return 0;
 }
 
-extern "C" int imparo_embed_copies(const void* table, int table_dtype, const int* ids, float scale, int copies, float* out,
+// pos_table: [n_positions, width] in the table's dtype with positions int32 [n_tok], or null (no position vectors).
+extern "C" int imparo_embed_copies(const void* table, int table_dtype, const int* ids, float scale, int copies,
+                                   const void* pos_table, const int* positions, int n_positions, float* out,
                                    int n_tok, int width, int vocab, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (copies < 1 || copies > HC_MAX) return -2;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == IMPARO_DT_F32)
-        launch(embed_copies_kernel<float>, dim3(n_tok), dim3(threads), 0, stream, (const float*)table, ids, scale, copies, out, width, vocab, status);
+        launch(embed_copies_kernel<float>, dim3(n_tok), dim3(threads), 0, stream, (const float*)table, ids, scale, copies,
+               (const float*)pos_table, positions, n_positions, out, width, vocab, status);
     else if (table_dtype == IMPARO_DT_BF16)
-        launch(embed_copies_kernel<__nv_bfloat16>, dim3(n_tok), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, scale, copies, out,
-               width, vocab, status);
+        launch(embed_copies_kernel<__nv_bfloat16>, dim3(n_tok), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, scale, copies,
+               (const __nv_bfloat16*)pos_table, positions, n_positions, out, width, vocab, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -133,7 +133,8 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_
 // the router matrix was cut into bfloat16 pieces whose sum is the 32-bit matrix to its last bit, see imparo_moe_pick)
 __global__ void __launch_bounds__(128)
 moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int parts, int top, int softmax_scores, int renormalise,
-                int* __restrict__ ids, float* __restrict__ wts) {
+                int groups, int keep, float renorm_eps, float weight_scale, int out_stride, int* __restrict__ ids,
+                float* __restrict__ wts) {
     extern __shared__ __align__(16) float pick_smem[];   // [4][experts]
     pdl_trigger();
     pdl_wait();
@@ -157,6 +158,34 @@ moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int p
         for (int e = lane; e < experts; e += 32) l += expf(s[e] - m);
         l = warp_sum(l);
     }
+    // Experts in `groups` equal groups of neighbours: a group's score is its largest, and only the `keep` best groups'
+    // experts stay candidates (ties: the lower group).  The others leave the candidates; the softmax above counted them.
+    if (groups > 1 && keep < groups) {
+        const int per = experts / groups;
+        // lane g (and g + 32, ...) finds group g's maximum; a group is kept when fewer than `keep` groups beat it.  All
+        // verdicts first, then the masking, so that every verdict reads the scores as they were.
+        unsigned long long drop = 0ull;                   // bit i: this lane's group lane + 32 i leaves (groups <= 2048)
+        for (int g0 = 0, it = 0; g0 < groups; g0 += 32, ++it) {
+            const int g = g0 + lane;
+            if (g >= groups) continue;
+            float mine = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) mine = fmaxf(mine, s[e]);
+            int beaten = 0;
+            for (int o = 0; o < groups; ++o) {
+                float other = -INFINITY;
+                for (int e = o * per; e < (o + 1) * per; ++e) other = fmaxf(other, s[e]);
+                if (other > mine || (other == mine && o < g)) ++beaten;
+            }
+            if (beaten >= keep) drop |= 1ull << it;
+        }
+        __syncwarp();
+        for (int g0 = 0, it = 0; g0 < groups; g0 += 32, ++it) {
+            const int g = g0 + lane;
+            if (g < groups && ((drop >> it) & 1ull))
+                for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -173,14 +202,20 @@ moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int p
         }
         const float score = softmax_scores ? expf(best - m) / l : 1.0f / (1.0f + expf(-best));
         if (lane == 0) {
-            ids[(size_t)r * top + k] = arg;
-            wts[(size_t)r * top + k] = score;
+            ids[(size_t)r * out_stride + k] = arg;
+            wts[(size_t)r * out_stride + k] = score;
             s[arg] = -INFINITY;
         }
         total += score;
         __syncwarp();
     }
-    if (renormalise && lane < top) wts[(size_t)r * top + lane] /= total;
+    if (renormalise && lane < top) wts[(size_t)r * out_stride + lane] = wts[(size_t)r * out_stride + lane] / (total + renorm_eps) * weight_scale;
+    else if (weight_scale != 1.0f && lane < top) wts[(size_t)r * out_stride + lane] *= weight_scale;
+    // choices beyond `top` (out_stride > top) are experts every row uses with weight 1: numbers experts, experts + 1, ...
+    for (int k = top + lane; k < out_stride; k += 32) {
+        ids[(size_t)r * out_stride + k] = experts + (k - top);
+        wts[(size_t)r * out_stride + k] = 1.0f;
+    }
 }
 
 // ---- (2) pair by pair ---------------------------------------------------------------------------------------------
@@ -221,7 +256,7 @@ __device__ __forceinline__ void warp_dot2(const T* __restrict__ w0, const T* __r
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids, const float* __restrict__ wts,
-                   int width, int ff, int top, int experts, int weight_input, T* __restrict__ mid) {
+                   int width, int ff, int top, int experts, int weight_input, int act, float limit, T* __restrict__ mid) {
     extern __shared__ __align__(16) float up_smem[];
     pdl_trigger();
     pdl_wait();
@@ -240,7 +275,7 @@ moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const in
         if (f >= ff) break;
         float ag, au;
         warp_dot2<T>(base + (size_t)f * width, base + (size_t)(ff + f) * width, up_smem, width, vec, lane, ag, au);
-        if (lane == 0) mid[(size_t)pair * ff + f] = from_f32<T>(silu(ag) * au);
+        if (lane == 0) mid[(size_t)pair * ff + f] = from_f32<T>(gated_act(act, limit, ag, au));
     }
 }
 
@@ -413,7 +448,8 @@ __device__ __forceinline__ void group_tile_product(GroupTile<T>& sm, LoadA load_
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_group_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ sorted, const int* __restrict__ plan,
-                    const float* __restrict__ wts, int width, int ff, int top, int weight_input, T* __restrict__ mid) {
+                    const float* __restrict__ wts, int width, int ff, int top, int weight_input, int act, float limit,
+                    T* __restrict__ mid) {
     __shared__ GroupTile<T> sm;
     __shared__ int pair_of[GM];
     __shared__ float wt_of[GM];
@@ -439,7 +475,7 @@ moe_group_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const i
     group_tile_product<T>(sm, load_a, base + (size_t)ff * width, n0, ff, width, rows);
     for (int i = threadIdx.x; i < GM * GN; i += 256) {
         const int m = i / GN, n = i % GN;
-        if (m < rows && n0 + n < ff) mid[(size_t)pair_of[m] * ff + n0 + n] = from_f32<T>(silu(gate_c[m][n]) * sm.c[m][n]);
+        if (m < rows && n0 + n < ff) mid[(size_t)pair_of[m] * ff + n0 + n] = from_f32<T>(gated_act(act, limit, gate_c[m][n], sm.c[m][n]));
     }
 }
 
@@ -592,10 +628,21 @@ moe_tile_sum_kernel(const float* __restrict__ out_g, const int* __restrict__ slo
 using namespace imparo;
 
 // logits: float32 scratch [n_rows, experts].  Two launches.
+// The choice's further parameters (both entry points): groups, keep (experts in `groups` equal groups of neighbours, only the
+// `keep` best groups' experts may be chosen; groups <= 1: all), renorm_eps (added to the chosen scores' sum before the
+// division when renormalise is set), weight_scale (a factor on the weights), out_stride (ids and wts have out_stride >= top
+// entries per row: the entries beyond `top` name experts every row uses with weight 1, numbered from `experts` on).
+static inline bool pick_args_ok(int experts, int top, int groups, int keep, int out_stride) {
+    if (top < 1 || top > experts || top > 32 || experts > 2048 || out_stride < top || out_stride > top + 32) return false;
+    if (groups > 1 && (experts % groups != 0 || keep < 1 || keep > groups || keep * (experts / groups) < top)) return false;
+    return true;
+}
+
 extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int n_rows, int width, int experts, int top,
-                                int softmax_scores, int renormalise, float* logits, int* ids, float* wts, cudaStream_t stream) {
+                                int softmax_scores, int renormalise, int groups, int keep, float renorm_eps, float weight_scale,
+                                int out_stride, float* logits, int* ids, float* wts, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (top < 1 || top > experts || top > 32 || experts > 2048 || logits == nullptr) return -2;
+    if (!pick_args_ok(experts, top, groups, keep, out_stride) || logits == nullptr) return -2;
     int per = 4;
     if ((size_t)4 * width * sizeof(float) > 48 * 1024) per = 1;
     const size_t smem = (size_t)per * width * sizeof(float);
@@ -609,7 +656,7 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
     else return -1;
     IMPARO_CHECK_LAUNCH();
     launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, (const float*)logits, n_rows,
-           experts, 1, top, softmax_scores, renormalise, ids, wts);
+           experts, 1, top, softmax_scores, renormalise, groups, keep, renorm_eps, weight_scale, out_stride, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
@@ -619,31 +666,32 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
 // rounded: 8 + 8 + 8 bits of mantissa, their sum is W to its last bit), the
 // tensor-core product h [w1; w2; w3]^T has exact products and 32-bit sums: the router's logits in 32-bit, at the product's speed.
 extern "C" int imparo_moe_pick(const float* logits, int n_rows, int experts, int parts, int top, int softmax_scores, int renormalise,
-                               int* ids, float* wts, cudaStream_t stream) {
+                               int groups, int keep, float renorm_eps, float weight_scale, int out_stride, int* ids, float* wts,
+                               cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (top < 1 || top > experts || top > 32 || experts > 2048 || parts < 1 || parts > 4) return -2;
+    if (!pick_args_ok(experts, top, groups, keep, out_stride) || parts < 1 || parts > 4) return -2;
     launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, logits, n_rows, experts,
-           parts, top, softmax_scores, renormalise, ids, wts);
+           parts, top, softmax_scores, renormalise, groups, keep, renorm_eps, weight_scale, out_stride, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
 
 // mid: [n_rows * top, ff] in dtype; out float32 [n_rows, width].  Two launches.
 extern "C" int imparo_moe_rows(const void* h, const void* w_gu, const void* w_down, int dtype, const int* ids, const float* wts,
-                               int n_rows, int width, int ff, int top, int experts, int weight_input, void* mid, float* out,
-                               cudaStream_t stream) {
+                               int n_rows, int width, int ff, int top, int experts, int weight_input, int act, float limit,
+                               void* mid, float* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if ((size_t)width * 4 > 48 * 1024 || (size_t)ff * 4 > 48 * 1024) return -25;
     dim3 g1(n_rows * top, (ff + 31) / 32), g2(n_rows, (width + 31) / 32);
     if (dtype == IMPARO_DT_F32) {
         launch(moe_rows_up_kernel<float>, g1, dim3(256), (size_t)width * 4, stream, (const float*)h, (const float*)w_gu, ids, wts, width,
-               ff, top, experts, weight_input, (float*)mid);
+               ff, top, experts, weight_input, act, limit, (float*)mid);
         IMPARO_CHECK_LAUNCH();
         launch(moe_rows_down_kernel<float>, g2, dim3(256), (size_t)ff * 4, stream, (const float*)mid, (const float*)w_down, ids, wts,
                width, ff, top, experts, weight_input, out);
     } else if (dtype == IMPARO_DT_BF16) {
         launch(moe_rows_up_kernel<__nv_bfloat16>, g1, dim3(256), (size_t)width * 4, stream, (const __nv_bfloat16*)h,
-               (const __nv_bfloat16*)w_gu, ids, wts, width, ff, top, experts, weight_input, (__nv_bfloat16*)mid);
+               (const __nv_bfloat16*)w_gu, ids, wts, width, ff, top, experts, weight_input, act, limit, (__nv_bfloat16*)mid);
         IMPARO_CHECK_LAUNCH();
         launch(moe_rows_down_kernel<__nv_bfloat16>, g2, dim3(256), (size_t)ff * 4, stream, (const __nv_bfloat16*)mid,
                (const __nv_bfloat16*)w_down, ids, wts, width, ff, top, experts, weight_input, out);
@@ -655,8 +703,8 @@ extern "C" int imparo_moe_rows(const void* h, const void* w_gu, const void* w_do
 // scratch_i: int32 [n_pairs + experts + 1 + 1 + 3 * max_tiles], max_tiles = n_pairs / 32 + experts; pair_out float32
 // [n_pairs, width]; mid [n_pairs, ff] in dtype; out float32 [n_rows, width].  Four launches.
 extern "C" int imparo_moe_grouped(const void* h, const void* w_gu, const void* w_down, int dtype, const int* ids, const float* wts,
-                                  int n_rows, int width, int ff, int top, int experts, int weight_input, void* mid,
-                                  float* pair_out, int* scratch_i, float* out, cudaStream_t stream) {
+                                  int n_rows, int width, int ff, int top, int experts, int weight_input, int act, float limit,
+                                  void* mid, float* pair_out, int* scratch_i, float* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int n_pairs = n_rows * top;
     const int max_tiles = n_pairs / GM + experts;
@@ -670,13 +718,13 @@ extern "C" int imparo_moe_grouped(const void* h, const void* w_gu, const void* w
     dim3 g1(max_tiles, (ff + GN - 1) / GN), g2(max_tiles, (width + GN - 1) / GN);
     if (dtype == IMPARO_DT_F32) {
         launch(moe_group_up_kernel<float>, g1, dim3(256), 0, stream, (const float*)h, (const float*)w_gu, (const int*)sorted,
-               (const int*)plan, wts, width, ff, top, weight_input, (float*)mid);
+               (const int*)plan, wts, width, ff, top, weight_input, act, limit, (float*)mid);
         IMPARO_CHECK_LAUNCH();
         launch(moe_group_down_kernel<float>, g2, dim3(256), 0, stream, (const float*)mid, (const float*)w_down, (const int*)sorted,
                (const int*)plan, wts, width, ff, weight_input, pair_out);
     } else if (dtype == IMPARO_DT_BF16) {
         launch(moe_group_up_kernel<__nv_bfloat16>, g1, dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu,
-               (const int*)sorted, (const int*)plan, wts, width, ff, top, weight_input, (__nv_bfloat16*)mid);
+               (const int*)sorted, (const int*)plan, wts, width, ff, top, weight_input, act, limit, (__nv_bfloat16*)mid);
         IMPARO_CHECK_LAUNCH();
         launch(moe_group_down_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, (const __nv_bfloat16*)mid, (const __nv_bfloat16*)w_down,
                (const int*)sorted, (const int*)plan, wts, width, ff, weight_input, pair_out);
@@ -690,15 +738,16 @@ extern "C" int imparo_moe_grouped(const void* h, const void* w_gu, const void* w
 }
 
 extern "C" int imparo_gemm_prefill_grouped(const void* x, int ldx, const void* w, int n_groups, void* out, int ldo, int m_tiles,
-                                           int N, int K, int epilogue, const int* tile_group, int* status, cudaStream_t stream);
+                                           int N, int K, int epilogue, int act, float limit, const int* tile_group, int* status,
+                                           cudaStream_t stream);
 
 // bfloat16, width and ff multiples of 8, at most 256 experts: rows sorted into tiles of 128 per expert and both products on
 // the tensor-memory kernel (SwiGLU in the first one's epilogue).  m_tiles = n_pairs / 128 + experts; xg bfloat16
 // [m_tiles * 128, width]; mid_g bfloat16 [m_tiles * 128, ff]; out_g float32 [m_tiles * 128, width]; scratch_i int32
 // [n_pairs + m_tiles]; out float32 [n_rows, width].  Five launches.  -25: not a case for this path.
 extern "C" int imparo_moe_tiles(const void* h, const void* w_gu, const void* w_down, const int* ids, const float* wts, int n_rows,
-                                int width, int ff, int top, int experts, int weight_input, void* xg, void* mid_g, float* out_g,
-                                int* scratch_i, float* out, int* status, cudaStream_t stream) {
+                                int width, int ff, int top, int experts, int weight_input, int act, float limit, void* xg, void* mid_g,
+                                float* out_g, int* scratch_i, float* out, int* status, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width % 8 != 0 || ff % 8 != 0 || experts > 256) return -25;
     const int n_pairs = n_rows * top;
@@ -711,9 +760,9 @@ extern "C" int imparo_moe_tiles(const void* h, const void* w_gu, const void* w_d
     launch(moe_tile_gather_kernel, dim3(n_pairs), dim3(128), 0, stream, (const __nv_bfloat16*)h, (const int*)slot_of_pair, wts, width,
            top, weight_input, (__nv_bfloat16*)xg);
     IMPARO_CHECK_LAUNCH();
-    int rc = imparo_gemm_prefill_grouped(xg, width, w_gu, experts, mid_g, ff, m_tiles, ff, width, 3, tile_group, status, stream);
+    int rc = imparo_gemm_prefill_grouped(xg, width, w_gu, experts, mid_g, ff, m_tiles, ff, width, 3, act, limit, tile_group, status, stream);
     if (rc) return rc;
-    rc = imparo_gemm_prefill_grouped(mid_g, ff, w_down, experts, out_g, width, m_tiles, width, ff, 1, tile_group, status, stream);
+    rc = imparo_gemm_prefill_grouped(mid_g, ff, w_down, experts, out_g, width, m_tiles, width, ff, 1, 0, 0.f, tile_group, status, stream);
     if (rc) return rc;
     launch(moe_tile_sum_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)out_g, (const int*)slot_of_pair, wts, width, top,
            weight_input, out);

@@ -255,6 +255,22 @@ __global__ void swiglu_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, _
     *reinterpret_cast<uint4*>(out + t * F + f) = r;
 }
 
+// ---- any gated activation of [gate | up] rows, with the two products' biases ------------------
+// gu: [T, 2F]; bias: float32 [2F] = [gate's | up's] or null; out: [T, F]; kind, limit: gated_act()
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, const float* __restrict__ bias, T* __restrict__ out, int n_tok, int F,
+                                 int kind, float limit) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_tok * F) return;
+    const size_t t = i / F, f = i % F;
+    float g = to_f32(gu[t * 2 * F + f]);
+    float u = to_f32(gu[t * 2 * F + F + f]);
+    if (bias) { g += bias[f]; u += bias[F + f]; }
+    out[i] = from_f32<T>(gated_act(kind, limit, g, u));
+}
+
 // ---- out[t, :] += bias ----------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n_tok, int width) {
@@ -406,6 +422,22 @@ extern "C" int imparo_swiglu_act(const void* gu, void* out, int dtype, int n_tok
                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
     else if (dtype == IMPARO_DT_BF16)
         launch(swiglu_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_gated_act(const void* gu, const float* bias, void* out, int dtype, int n_tok, int F, int kind, float limit,
+                                cudaStream_t stream) {
+    if (n_tok <= 0 || F <= 0) return 0;
+    if (kind < 0 || kind > 2) return -2;
+    const size_t n = (size_t)n_tok * F;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (dtype == IMPARO_DT_F32)
+        launch(gated_act_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, bias, (float*)out, n_tok, F, kind, limit);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(gated_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, bias, (__nv_bfloat16*)out, n_tok, F,
+               kind, limit);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

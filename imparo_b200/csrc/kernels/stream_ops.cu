@@ -252,6 +252,21 @@ __global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict
         x[i] += coef * y[i];
 }
 
+// x += sum_b coef[b] * y_b for up to four float32 sources of x's shape, in the order b = 0, 1, ...
+__global__ void add_weighted_kernel(float* __restrict__ x, Branches br, int n_branches, float c0, float c1, float c2, float c3,
+                                    size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const float c[4] = {c0, c1, c2, c3};
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (b < n_branches) acc += c[b] * br.b[b][i];
+        x[i] += acc;
+    }
+}
+
 // x[t, :] += (table[ids[t], :] if table) + (vec[:] if vec)
 template <typename T>
 __global__ void stream_inject_kernel(float* __restrict__ x, const T* __restrict__ table, const int* __restrict__ ids,
@@ -447,6 +462,18 @@ extern "C" int imparo_norm_mean_add_rmsnorm(float* x, int n_branches, const floa
 extern "C" int imparo_add_scaled(float* x, const float* y, float coef, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     launch(add_scaled_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, x, y, coef, (size_t)n);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// ys: up to four float32 device pointers of n floats each (null beyond n_branches); coefs: their factors.
+extern "C" int imparo_add_weighted(float* x, const float* y0, const float* y1, const float* y2, const float* y3, int n_branches,
+                                   float c0, float c1, float c2, float c3, long long n, cudaStream_t stream) {
+    if (n <= 0 || n_branches <= 0) return 0;
+    if (n_branches > 4) return -2;
+    Branches br;
+    br.b[0] = y0; br.b[1] = y1; br.b[2] = y2; br.b[3] = y3;
+    launch(add_weighted_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, x, br, n_branches, c0, c1, c2, c3, (size_t)n);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -72,6 +72,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_add_partials_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_swiglu_act", [P, P, I, I, I, S])
     _declare(lib, "imparo_add_bias", [P, I, P, I, I, S])
+    _declare(lib, "imparo_gated_act", [P, P, P, I, I, I, I, c_float, S])
     _declare(lib, "imparo_sgemm_nt", [P, P, P, I, I, I, I, I, I, S])
     _declare(lib, "imparo_gemm_lib_init", [P, c_size_t])
     _declare(lib, "imparo_gemm_bf16_nt", [P, P, P, I, I, I, I, I, I, I, S])
@@ -96,8 +97,8 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_attention_split_combine_sinks", [P, P, P, I, I, I, I, P, I, S])
     _declare(lib, "imparo_attention_prefill_tc_sinks",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, c_float, P, P, I, I, I, I, I, P, S])
-    _declare(lib, "imparo_gemm_bf16_heads", [P, P, P, I, I, I, I, I, I, S])
-    _declare(lib, "imparo_sigmoid_gate", [P, c_int64, P, c_int64, I, I, I, S])
+    _declare(lib, "imparo_gemm_bf16_heads", [P, P, P, I, I, I, I, I, I, I, I, S])
+    _declare(lib, "imparo_sigmoid_gate", [P, c_int64, P, c_int64, I, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma_qkv",
              [P, I, c_int64, P, P, P, I, c_float, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
@@ -119,6 +120,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_norm_mean_add", [P, I, P, P, c_float, c_float, P, c_float, I, I, S])
     _declare(lib, "imparo_norm_mean_add_rmsnorm", [P, I, P, P, c_float, c_float, P, c_float, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_add_scaled", [P, P, c_float, c_int64, S])
+    _declare(lib, "imparo_add_weighted", [P, P, P, P, P, I, c_float, c_float, c_float, c_float, c_int64, S])
     _declare(lib, "imparo_stream_inject", [P, P, I, P, P, I, I, I, P, S])
     _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])
     _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
@@ -132,22 +134,25 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_mamba2_scan", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, P, S])
     _declare(lib, "imparo_mamba2_scan_chunked", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_gate_group_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, I, S])
-    _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, P, S])
-    _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, S])
-    _declare(lib, "imparo_moe_pick", [P, I, I, I, I, I, I, P, P, S])
-    _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, S])
-    _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])
+    _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, I, I, c_float, c_float, I, P, P, P, S])
+    _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, I, c_float, P, P, S])
+    _declare(lib, "imparo_moe_pick", [P, I, I, I, I, I, I, I, I, c_float, c_float, I, P, P, S])
+    _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, I, c_float, P, P, P, P, P, P, S])
+    _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, I, c_float, P, P, P, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
     _declare(lib, "imparo_streams_norm", [P, P, I, P, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_streams_mix_add", [P, I, P, P, P, P, P, c_float, P, I, I, I, S])
-    _declare(lib, "imparo_embed_copies", [P, I, P, c_float, I, P, I, I, I, P, S])
+    _declare(lib, "imparo_embed_copies", [P, I, P, c_float, I, P, P, I, P, I, I, I, P, S])
     _declare(lib, "imparo_channel_conv", [P, c_int64, I, I, I, P, P, P, P, P, P, I, I, P, c_int64, I, P, S])
     _declare(lib, "imparo_channel_conv_state", [P, c_int64, I, I, I, P, P, P, P, I, I, S])
     _declare(lib, "imparo_delta_prepare", [P, c_int64, I, I, P, c_int64, I, P, P, P, P, I, I, I, I, c_float, c_float, S])
     _declare(lib, "imparo_delta_scan", [P, c_int64, I, I, I, P, P, P, P, P, I, I, P, I, I, I, I, P, S])
-    _declare(lib, "imparo_head_norm_gate", [P, P, c_float, P, c_int64, P, I, I, I, I, S])
+    _declare(lib, "imparo_head_norm_gate", [P, P, c_float, P, c_int64, P, I, I, I, I, I, S])
     _declare(lib, "imparo_latent_norm_store", [P, c_int64, I, I, I, I, P, P, c_float, P, P, P, P, I, P, I, I, I, I, P, S])
-    _declare(lib, "imparo_heads_linear", [P, c_int64, P, P, c_int64, P, c_int64, I, I, I, I, I, S])
+    _declare(lib, "imparo_latent_rot_store", [P, c_int64, I, I, I, I, P, c_float, P, I, P, P, P, P, P, I, P, I, I, I, I, P, S])
+    _declare(lib, "imparo_mlstm_scan", [P, c_int64, I, I, I, I, I, P, P, c_float, c_float, P, P, P, P, P, I, I, I, P, I, I, I, I, P, P, P,
+                                        P, S])
+    _declare(lib, "imparo_heads_linear", [P, c_int64, P, P, c_int64, P, c_int64, I, I, I, I, I, I, I, I, S])
     _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])
 
 

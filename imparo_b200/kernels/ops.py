@@ -298,6 +298,24 @@ def swiglu_act(gu: torch.Tensor, out: torch.Tensor) -> None:
     _check(_lib.kernels().imparo_swiglu_act(_ptr(gu), _ptr(out), _code(out), n, F, _stream()), "swiglu_act")
 
 
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: float = 0.0, bias: Optional[torch.Tensor] = None) -> None:
+    """out[T, F] = act(gate, up) of gu = [gate | up] rows ([T, 2F]), after adding bias (float32 [2F]) when given.
+    kind: "silu" silu(g) u; "gelu_tanh" gelu(g) u; "clamped_swish" with g' = min(g, limit), u' = clamp(u, -limit, limit):
+    g' sigmoid(1.702 g') (u' + 1)."""
+    _cuda(gu, out)
+    _need(kind in GATED_ACTIVATIONS, f"gated_act: unknown kind '{kind}' (known: {', '.join(sorted(GATED_ACTIVATIONS))})")
+    n, F = out.shape
+    _need(gu.shape == (n, 2 * F) and gu.dtype == out.dtype, "gated_act: gu must be [tokens, 2F] of the output dtype")
+    if bias is not None:
+        _cuda(bias)
+        _need(bias.dtype == torch.float32 and bias.numel() == 2 * F, "gated_act: bias float32 [2F]")
+    _check(_lib.kernels().imparo_gated_act(_ptr(gu), _ptr(bias), _ptr(out), _code(out), n, F, GATED_ACTIVATIONS[kind], float(limit),
+                                           _stream()), "gated_act")
+
+
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     _cuda(out, bias)
     settle(out)
@@ -475,6 +493,18 @@ def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[tor
     _need(tmp is not None and tmp.shape == (x.shape[0], w_gu.shape[0]), "linear_swiglu: tmp [T, 2F] needed on this path")
     linear(x, w_gu, tmp)
     swiglu_act(tmp, out)
+
+
+def linear_gated(x, w_gu: torch.Tensor, out: torch.Tensor, kind: str, limit: float = 0.0, bias: Optional[torch.Tensor] = None,
+                 status: Optional[torch.Tensor] = None, tmp=None) -> None:
+    """out[T, F] = act(x gate^T + b_g, x up^T + b_u) with w_gu = [gate; up] ([2F, K]), bias float32 [2F] or None, for the
+    gated activations of gated_act: the product into tmp [T, 2F] (a tensor, or a function that makes it), then one kernel
+    that adds the biases and applies the activation."""
+    if callable(tmp):
+        tmp = tmp()
+    _need(tmp is not None and tmp.shape == (x.shape[0], w_gu.shape[0]), "linear_gated: tmp [T, 2F] needed")
+    linear(x, w_gu, tmp, status=status)
+    gated_act(tmp, out, kind, limit, bias)
 
 
 def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
@@ -1094,6 +1124,19 @@ def add_scaled(x: torch.Tensor, y: torch.Tensor, coef: float) -> None:
     _check(_lib.kernels().imparo_add_scaled(_ptr(x), _ptr(y), float(coef), x.numel(), _stream()), "add_scaled")
 
 
+def add_weighted(x: torch.Tensor, ys, coefs) -> None:
+    """x += sum_b coefs[b] * ys[b] for one to four float32 tensors of x's shape, in one pass over x."""
+    settle(x)
+    _cuda(x, *ys)
+    _need(1 <= len(ys) <= 4 and len(coefs) == len(ys), "add_weighted: one to four sources, a factor each")
+    _need(x.dtype == torch.float32 and x.is_contiguous() and all(y.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous() for y in ys),
+          "add_weighted: float32 tensors of one shape")
+    p = [_ptr(y) for y in ys] + [None] * (4 - len(ys))
+    c = [float(v) for v in coefs] + [0.0] * (4 - len(ys))
+    _check(_lib.kernels().imparo_add_weighted(_ptr(x), p[0], p[1], p[2], p[3], len(ys), c[0], c[1], c[2], c[3], x.numel(), _stream()),
+           "add_weighted")
+
+
 def stream_inject(x: torch.Tensor, table: Optional[torch.Tensor], ids: Optional[torch.Tensor], vec: Optional[torch.Tensor],
                   status: torch.Tensor) -> None:
     """x[t] += table[ids[t]] (when table is given) + vec (when given).  x: float32 [tokens, width]."""
@@ -1343,10 +1386,22 @@ def gate_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: f
 
 
 # ---- routed feed-forward (csrc/kernels/moe.cu) -------------------------------------------------------------------
+def _pick_args(top, ids, wts, n, groups, keep, always):
+    stride = int(top) + int(always)
+    _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * stride and wts.numel() >= n * stride,
+          "moe: ids int32 and wts float32 [rows, top + always]")
+    return int(groups), int(keep if keep else groups), stride
+
+
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, softmax: bool = False,
-              renormalise: bool = False, logits: Optional[torch.Tensor] = None) -> None:
+              renormalise: bool = False, logits: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 0,
+              renorm_eps: float = 0.0, weight_scale: float = 1.0, always: int = 0) -> None:
     """Router logits W_r h in 32-bit, sigmoid (or softmax) scores, the `top` largest per row: ids int32 [rows, top],
-    wts float32 [rows, top].  logits: float32 scratch [rows, experts] (made here when not given)."""
+    wts float32 [rows, top].  logits: float32 scratch [rows, experts] (made here when not given).
+    groups, keep: the experts form `groups` equal groups of neighbours, a group's score is its largest, and only the `keep`
+    best groups' experts can be chosen.  renormalise divides the chosen scores by their sum + renorm_eps; weight_scale
+    multiplies the weights.  always = a: ids and wts are [rows, top + a], the last a entries name experts number
+    experts, experts + 1, ... with weight 1 (experts every row uses, stacked behind the routed ones)."""
     n, width = h.shape
     E = w_router.shape[0]
     if logits is None:
@@ -1354,24 +1409,26 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tens
     _cuda(h, w_router, ids, wts, logits)
     _need(logits.dtype == torch.float32 and logits.numel() >= n * E, "moe_route: logits float32 [rows, experts]")
     _need(w_router.dtype == torch.float32 and w_router.shape[1] == width, "moe_route: router float32 [experts, width]")
-    _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * top and wts.numel() >= n * top,
-          "moe_route: ids int32 and wts float32 [rows, top]")
+    groups, keep, stride = _pick_args(top, ids, wts, n, groups, keep, always)
     _check(_lib.kernels().imparo_moe_route(_ptr(h), _code(h), _ptr(w_router), n, width, E, int(top), int(bool(softmax)),
-                                           int(bool(renormalise)), _ptr(logits), _ptr(ids), _ptr(wts), _stream()), "moe_route")
+                                           int(bool(renormalise)), groups, keep, float(renorm_eps), float(weight_scale), stride,
+                                           _ptr(logits), _ptr(ids), _ptr(wts), _stream()), "moe_route")
     COUNTS["own"] += 1
 
 
 def moe_pick(logits: torch.Tensor, experts: int, parts: int, top: int, ids: torch.Tensor, wts: torch.Tensor, softmax: bool = False,
-             renormalise: bool = False) -> None:
+             renormalise: bool = False, groups: int = 1, keep: int = 0, renorm_eps: float = 0.0, weight_scale: float = 1.0,
+             always: int = 0) -> None:
     """The router's choice from logits a product has made: logits float32 [rows, parts * experts], a logit being the sum of
-    its `parts` entries `experts` apart (a 32-bit router matrix cut into bfloat16 pieces that add up to it to its last bit)."""
+    its `parts` entries `experts` apart (a 32-bit router matrix cut into bfloat16 pieces that add up to it to its last bit).
+    groups, keep, renorm_eps, weight_scale, always: as for moe_route."""
     _cuda(logits, ids, wts)
     n = logits.shape[0]
     _need(logits.dtype == torch.float32 and logits.shape[1] == parts * experts, "moe_pick: logits float32 [rows, parts * experts]")
-    _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * top and wts.numel() >= n * top,
-          "moe_pick: ids int32 and wts float32 [rows, top]")
+    groups, keep, stride = _pick_args(top, ids, wts, n, groups, keep, always)
     _check(_lib.kernels().imparo_moe_pick(_ptr(logits), n, int(experts), int(parts), int(top), int(bool(softmax)),
-                                          int(bool(renormalise)), _ptr(ids), _ptr(wts), _stream()), "moe_pick")
+                                          int(bool(renormalise)), groups, keep, float(renorm_eps), float(weight_scale), stride,
+                                          _ptr(ids), _ptr(wts), _stream()), "moe_pick")
 
 
 MOE_GROUP_FROM = 32          # steps with at least this many (row, choice) pairs per expert on average run grouped by expert
@@ -1385,7 +1442,7 @@ def moe_tiles_usable(h: torch.Tensor, w_gu: torch.Tensor) -> bool:
 
 def moe_experts_tiles(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int,
                       weight_input: bool, xg: torch.Tensor, mid_g: torch.Tensor, out_g: torch.Tensor, scratch_i: torch.Tensor,
-                      out: torch.Tensor, status: torch.Tensor) -> None:
+                      out: torch.Tensor, status: torch.Tensor, act: str = "silu", limit: float = 0.0) -> None:
     """The same result as moe_experts for steps of many rows in bfloat16: the (row, choice) pairs are sorted by expert into
     a buffer in which every expert's rows start at a multiple of 128 (xg, inputs already weighted), and both products run
     on the persistent tensor-memory kernel in its grouped form (silu(gate) * up in the first one's epilogue).  With
@@ -1404,14 +1461,15 @@ def moe_experts_tiles(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
           "moe_experts_tiles: scratch too small")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (n, width), "moe_experts_tiles: out float32 [rows, width]")
     _check(_lib.kernels().imparo_moe_tiles(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(wts), n, width, ff, int(top), E,
-                                           int(bool(weight_input)), _ptr(xg), _ptr(mid_g), _ptr(out_g), _ptr(scratch_i), _ptr(out),
-                                           _ptr(status), _stream()), "moe_tiles")
+                                           int(bool(weight_input)), GATED_ACTIVATIONS[act], float(limit), _ptr(xg), _ptr(mid_g),
+                                           _ptr(out_g), _ptr(scratch_i), _ptr(out), _ptr(status), _stream()), "moe_tiles")
     COUNTS["own"] += 4
 
 
 def moe_experts(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int,
-                weight_input: bool, mid: torch.Tensor, out: torch.Tensor, scratch=None) -> None:
+                weight_input: bool, mid: torch.Tensor, out: torch.Tensor, scratch=None, act: str = "silu", limit: float = 0.0) -> None:
     """out[r] = sum_k expert_{ids[r,k]}(wts[r,k] * h[r])  (weight_input) or sum_k wts[r,k] * expert(h[r]).
+    act, limit: the experts' gated activation (gated_act's kinds).
     w_gu [experts, 2 ff, width] = [gate; up], w_down [experts, width, ff]; mid [rows*top, ff] in h's dtype; out float32
     [rows, width], overwritten.  scratch = (float32 [rows*top, width], int32 [rows*top + experts + 2 + 3*(rows*top//32 + experts)]):
     when given, pairs are sorted by expert and run as tiles (steps of many rows); else each pair on its own."""
@@ -1428,20 +1486,28 @@ def moe_experts(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: 
         _need(pair_out.dtype == torch.float32 and pair_out.numel() >= n * top * width and si.dtype == torch.int32
               and si.numel() >= n * top + E + 2 + 3 * (n * top // 32 + E), "moe_experts: grouped scratch too small")
         _check(_lib.kernels().imparo_moe_grouped(_ptr(h), _ptr(w_gu), _ptr(w_down), _code(h), _ptr(ids), _ptr(wts), n, width, ff, int(top),
-                                                 E, int(bool(weight_input)), _ptr(mid), _ptr(pair_out), _ptr(si), _ptr(out), _stream()),
+                                                 E, int(bool(weight_input)), GATED_ACTIVATIONS[act], float(limit), _ptr(mid), _ptr(pair_out),
+                                                 _ptr(si), _ptr(out), _stream()),
                "moe_grouped")
         COUNTS["own"] += 3
         return
     _check(_lib.kernels().imparo_moe_rows(_ptr(h), _ptr(w_gu), _ptr(w_down), _code(h), _ptr(ids), _ptr(wts), n, width, ff, int(top), E,
-                                          int(bool(weight_input)), _ptr(mid), _ptr(out), _stream()), "moe_rows")
+                                          int(bool(weight_input)), GATED_ACTIVATIONS[act], float(limit), _ptr(mid), _ptr(out), _stream()),
+           "moe_rows")
     COUNTS["own"] += 1
 
 
 # ---- a stream kept as n copies per token (csrc/kernels/hyper_connections.cu) -----------------------------------
 def embed_copies(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor, scale: float = 1.0,
-                 copies: int = 1) -> None:
-    """out [T, copies * width] float32: the embedding row times scale, written into every copy."""
+                 copies: int = 1, pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+    """out [T, copies * width] float32: the embedding row times scale, plus (with pos_table [n, width] and positions
+    int32 [T]) the unscaled row of the token's position, written into every copy."""
     _cuda(table, ids, out, status)
+    if pos_table is not None:
+        _cuda(pos_table, positions)
+        _need(pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[1] == table.shape[1],
+              "position table: the embedding table's dtype and width")
+        _need(positions.dtype == torch.int32 and positions.numel() >= out.shape[0], "positions must be int32, one per output row")
     for d in (_S.pending, _S.pending_mean, _S.pending_mix):      # the stream starts afresh
         d.pop(out.data_ptr(), None)
     n = out.shape[0]
@@ -1449,7 +1515,8 @@ def embed_copies(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
     _need(out.dtype == torch.float32 and out.shape[1] == copies * width and out.is_contiguous(),
           "embedding output is float32 [tokens, copies * width]")
-    _check(_lib.kernels().imparo_embed_copies(_ptr(table), _code(table), _ptr(ids), float(scale), int(copies), _ptr(out), n, width,
+    _check(_lib.kernels().imparo_embed_copies(_ptr(table), _code(table), _ptr(ids), float(scale), int(copies), _ptr(pos_table),
+                                              _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, _ptr(out), n, width,
                                               table.shape[0], _ptr(status), _stream()), "embed_copies")
 
 
@@ -1573,17 +1640,69 @@ def delta_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, g: torch.T
 
 
 def head_norm_gate(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int, vdim: int) -> None:
-    """out[t, h] = o[t, h] / rms(o[t, h]) * w * sigmoid(gate[t, h]) per head.  o float32 [T, heads * vdim]; w float32 [vdim];
-    gate float32 rows (dense, any row stride)."""
+    """out[t, h] = o[t, h] / rms(o[t, h]) * w * sigmoid(gate[t, h]) per head.  o float32 [T, heads * vdim]; w float32 [vdim]
+    (one weight shared by the heads) or [heads * vdim] (each head's own); gate float32 rows (dense, any row stride)."""
     _cuda(o, w, out)
     _need(gate.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     T = o.shape[0]
     _need(o.dtype == torch.float32 and o.is_contiguous() and tuple(o.shape) == (T, heads * vdim), "head_norm_gate: o float32 [T, heads * vdim]")
-    _need(w.dtype == torch.float32 and w.numel() == vdim, "head_norm_gate: weight float32 [vdim]")
+    _need(w.dtype == torch.float32 and w.numel() in (vdim, heads * vdim), "head_norm_gate: weight float32 [vdim] or [heads * vdim]")
     _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (T, heads * vdim), "head_norm_gate: gate float32")
     _need(out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "head_norm_gate: out [T, heads * vdim]")
     _check(_lib.kernels().imparo_head_norm_gate(_ptr(o), _ptr(w), float(eps), _ptr(gate), gate.stride(0), _ptr(out), _code(out), T,
-                                                heads, vdim, _stream()), "head_norm_gate")
+                                                heads, vdim, vdim if w.numel() == heads * vdim and heads > 1 else 0, _stream()),
+           "head_norm_gate")
+
+
+# ---- a matrix memory with exponential gates (csrc/kernels/mlstm.cu) ---------------------------------------------
+def mlstm_value_blocks(vdim: int) -> int:
+    """How many copies of n and m a head keeps in its slot: one per 32 value columns (one per warp of the recurrence)."""
+    return (int(vdim) + 31) // 32
+
+
+def mlstm_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, cap: float, q_scale: float, state_S: torch.Tensor, state_n: torch.Tensor, state_m: torch.Tensor,
+               item_row_start, item_slot, n_items: int, out: torch.Tensor, heads: int, dim: int, vdim: int, status: torch.Tensor,
+               chunk: int = 0, scratch=None) -> None:
+    """Per request and head, over the request's rows in order, from and into its slot:
+    a = cap tanh((x_i + b_i) / cap), f = log sigmoid(cap tanh((x_f + b_f) / cap)), m' = max(f + m, a),
+    S' = exp(f + m - m') S + exp(a - m') k v^T, n' alike with k alone, o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6), q times
+    q_scale.  proj: float32 rows holding q, k (heads * dim each), v (heads * vdim) and the gates' inputs (heads each) at the
+    given column offsets; biases float32 [heads].  With vb = mlstm_value_blocks(vdim): state_S float32 [slots, heads, dim,
+    vdim], state_n [slots, heads, vb, dim], state_m [slots, heads, vb]; out float32 [T, heads * vdim].
+
+    chunk > 0 (batches with long portions): a request's rows are cut into chunks of that many rows which run side by side
+    (three launches); scratch = (S, n, mb) float32 for (T // chunk + n_items) chunks: heads * dim * vdim, heads * vb * dim and
+    heads * vb * 3 values per chunk.  The result differs from the row-by-row walk by the order of 32-bit additions only."""
+    _need(proj.is_cuda and proj.stride(1) == 1 and proj.dtype == torch.float32, "mlstm_scan: a float32 product with dense rows")
+    _cuda(i_bias, f_bias, state_S, state_n, state_m, item_row_start, item_slot, out, status)
+    T = proj.shape[0]
+    vb = mlstm_value_blocks(vdim)
+    _need(1 <= dim <= 256 and heads >= 1 and vdim >= 1 and cap > 0.0, "mlstm_scan: key size 1 to 256, a positive gate cap")
+    _need(max(q_off, k_off) + heads * dim <= proj.shape[1] and v_off + heads * vdim <= proj.shape[1]
+          and max(i_off, f_off) + heads <= proj.shape[1], "mlstm_scan: column ranges")
+    _need(i_bias.dtype == torch.float32 and f_bias.dtype == torch.float32 and i_bias.numel() == heads and f_bias.numel() == heads,
+          "mlstm_scan: gate biases float32 [heads]")
+    n_slots = state_S.shape[0]
+    _need(state_S.dtype == torch.float32 and state_S.is_contiguous() and tuple(state_S.shape[1:]) == (heads, dim, vdim)
+          and state_n.dtype == torch.float32 and state_n.is_contiguous() and tuple(state_n.shape) == (n_slots, heads, vb, dim)
+          and state_m.dtype == torch.float32 and state_m.is_contiguous() and tuple(state_m.shape) == (n_slots, heads, vb),
+          "mlstm_scan: state tensors float32 [slots, heads, dim, vdim], [slots, heads, vb, dim], [slots, heads, vb]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "mlstm_scan: out float32 [T, heads * vdim]")
+    _need(item_row_start.dtype == torch.int32 and item_slot.dtype == torch.int32 and item_row_start.numel() >= n_items + 1
+          and item_slot.numel() >= n_items and n_items <= 65535, "mlstm_scan: item arrays int32")
+    cS = cn = cmb = None
+    if chunk > 0:
+        cS, cn, cmb = scratch
+        _cuda(cS, cn, cmb)
+        most = T // chunk + n_items
+        _need(cS.dtype == cn.dtype == cmb.dtype == torch.float32 and cS.numel() >= most * heads * dim * vdim
+              and cn.numel() >= most * heads * vb * dim and cmb.numel() >= most * heads * vb * 3, "mlstm_scan: chunk scratch too small")
+    _check(_lib.kernels().imparo_mlstm_scan(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), int(i_off), int(f_off),
+                                            _ptr(i_bias), _ptr(f_bias), float(cap), float(q_scale), _ptr(state_S), _ptr(state_n),
+                                            _ptr(state_m), _ptr(item_row_start), _ptr(item_slot), n_slots, int(n_items), T, _ptr(out),
+                                            heads, dim, vdim, int(chunk), _ptr(cS), _ptr(cn), _ptr(cmb), _ptr(status), _stream()),
+           "mlstm_scan")
 
 
 # ---- attention over cached latent vectors (csrc/kernels/latent.cu) ----------------------------------------------
@@ -1608,31 +1727,76 @@ def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, c
                                                    _stream()), "latent_norm_store")
 
 
+def latent_rot_store(proj: torch.Tensor, heads: int, dim: int, rot: int, rank: int, wc: torch.Tensor, eps: float,
+                     inv_freq: Optional[torch.Tensor], n_rot: int, positions, item_of_token, q_plain: torch.Tensor,
+                     q_lat: torch.Tensor, cache: torch.Tensor, table, page_size: int, n_pages: int, status: torch.Tensor) -> None:
+    """The latent attention's row preparation when a rotated part stands beside the latent.  proj: a 32-bit product's rows
+    [heads x (dim | rot) | rank | rot | ...].  The page row becomes [rms(latent) * wc | turned key part] (rank + rot wide);
+    q_plain [T, heads * dim] gets every head's plain query dimensions, q_lat [T, heads * (rank + rot)] the turned ones in each
+    head's last rot entries.  The turn is the half-split rotation of the first n_rot of the rot dimensions by
+    position * inv_freq (float32 [n_rot / 2])."""
+    _cuda(wc, positions, item_of_token, q_plain, q_lat, cache, table, status)
+    _need(proj.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T = q_plain.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[0] == T and proj.shape[1] >= heads * (dim + rot) + rank + rot,
+          "latent_rot_store: a float32 product with dense rows [heads * (dim + rot) + rank + rot]")
+    _need(wc.dtype == torch.float32 and wc.numel() == rank, "latent_rot_store: norm weight float32 [rank]")
+    _need(q_plain.is_contiguous() and tuple(q_plain.shape) == (T, heads * dim) and q_lat.is_contiguous()
+          and tuple(q_lat.shape) == (T, heads * (rank + rot)) and q_plain.dtype == q_lat.dtype == cache.dtype, "latent_rot_store: outputs")
+    _need(n_rot == 0 or (inv_freq is not None and inv_freq.is_cuda and inv_freq.dtype == torch.float32 and inv_freq.numel() == n_rot // 2
+                         and n_rot % 2 == 0 and n_rot <= rot), "latent_rot_store: rotation table float32 [n_rot / 2]")
+    _need(cache.numel() >= n_pages * page_size * (rank + rot), "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _check(_lib.kernels().imparo_latent_rot_store(_ptr(proj), proj.stride(0), heads, dim, rot, rank, _ptr(wc), float(eps),
+                                                  _ptr(inv_freq) if n_rot else None, int(n_rot), _ptr(positions), _ptr(item_of_token),
+                                                  _ptr(q_plain), _ptr(q_lat), _ptr(cache), _code(q_plain), _ptr(table), table.shape[1],
+                                                  page_size, n_pages, T, _ptr(status), _stream()), "latent_rot_store")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> None:
+    """x[t, c] *= sigmoid(gate[t, c // group]) in place.  x [T, width] (rows dense, bfloat16 or float32); gate float32
+    [T, width // group] (rows dense, any row stride: columns of a 32-bit product)."""
+    _need(x.is_cuda and gate.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    T, width = x.shape
+    _need(x.stride(1) == 1 and gate.dtype == torch.float32 and gate.stride(1) == 1 and group >= 1 and width % group == 0
+          and tuple(gate.shape) == (T, width // group), "sigmoid_gate: gate float32 [T, width / group]")
+    _check(_lib.kernels().imparo_sigmoid_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _code(x), T, width, int(group),
+                                              _stream()), "sigmoid_gate")
+
+
 HEADS_LINEAR_LIBRARY_ROWS = 64          # from this many rows on the per-head products go to the library in one batched call
 
 
-def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
-    """out[t, h, :] = w[h] x[t, h, :] for every head (w [heads, n_out, n_in]; x [T, heads * n_in], out [T, heads * n_out],
-    rows dense), optionally times sigmoid(gate[t, h, :]) (float32 [T, heads * n_out], rows dense).  32-bit sums."""
+def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                 x_head: Optional[int] = None, out_head: Optional[int] = None) -> None:
+    """out[t, h, :] = w[h] x[t, h, :] for every head (w [heads, n_out, n_in]; rows dense), optionally times a sigmoid gate:
+    gate float32 [T, heads * n_out] (an own gate per output) or [T, heads] (one per head), rows dense.  Head h's inputs start
+    at column h * x_head of x (default n_in: x is [T, heads * n_in]) and its outputs at column h * out_head of out (default
+    n_out); with wider heads the other columns of out are left as they are.  32-bit sums."""
     _cuda(w)
     _need(x.is_cuda and out.is_cuda and (gate is None or gate.is_cuda), "kernels run on CUDA tensors only (there is no CPU path)")
     heads, n_out, n_in = w.shape
     T = x.shape[0]
+    x_head = n_in if x_head is None else int(x_head)
+    out_head = n_out if out_head is None else int(out_head)
     _need(x.dtype == w.dtype == out.dtype and w.is_contiguous(), "heads_linear: one dtype, dense weights")
-    _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(x.shape) == (T, heads * n_in) and tuple(out.shape) == (T, heads * n_out),
-          "heads_linear: shapes")
-    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == (T, heads * n_out)),
-          "heads_linear: gate float32 [T, heads * n_out]")
+    _need(x.stride(1) == 1 and out.stride(1) == 1 and x_head >= n_in and out_head >= n_out and tuple(x.shape) == (T, heads * x_head)
+          and tuple(out.shape) == (T, heads * out_head), "heads_linear: shapes")
+    per_head = gate is not None and gate.shape[1] == heads and n_out != 1
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) in ((T, heads * n_out), (T, heads))),
+          "heads_linear: gate float32 [T, heads * n_out] or [T, heads]")
     if x.dtype == torch.bfloat16 and T >= HEADS_LINEAR_LIBRARY_ROWS and n_in % 8 == 0 and n_out % 8 == 0 \
-            and x.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+            and x.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and x_head % 8 == 0 and out_head % 8 == 0 \
+            and (gate is None or out_head == n_out):
         # many rows: one batched library product over the heads (tensor cores, 32-bit sums), then the gate in place
         _gemm_lib_ready(x.device)
         _check(_lib.kernels().imparo_gemm_bf16_heads(_ptr(x), _ptr(w), _ptr(out), T, heads, n_out, n_in, x.stride(0), out.stride(0),
-                                                     _stream()), "gemm_bf16_heads", "library")
+                                                     x_head, out_head, _stream()), "gemm_bf16_heads", "library")
         if gate is not None:
             _check(_lib.kernels().imparo_sigmoid_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), _code(out), T,
-                                                      heads * n_out, _stream()), "sigmoid_gate")
+                                                      heads * n_out, n_out if per_head else 1, _stream()), "sigmoid_gate")
         return
     _need(n_in * 32 <= 48 * 1024, "heads_linear: input size per head up to 1536")
     _check(_lib.kernels().imparo_heads_linear(_ptr(x), x.stride(0), _ptr(w), _ptr(gate), gate.stride(0) if gate is not None else 0,
-                                              _ptr(out), out.stride(0), _code(x), T, heads, n_in, n_out, _stream()), "heads_linear")
+                                              _ptr(out), out.stride(0), _code(x), T, heads, n_in, n_out, x_head, out_head,
+                                              int(per_head), _stream()), "heads_linear")

@@ -3,3 +3,4 @@ from . import lfm2  # noqa: F401
 from . import vipotar  # noqa: F401
 from . import negotar  # noqa: F401
 from . import keralix  # noqa: F401
+from . import zepesun  # noqa: F401

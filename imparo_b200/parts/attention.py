@@ -31,7 +31,10 @@ class AttentionMixer(Part):
     lambda its own scalar tensor), qk_conv ({"taps": n, "q": tensor name, "k": tensor name}: a causal convolution over time on
     every channel of q and of k, taps [channels, n] with the last column on the current token, right after the projection
     and its bias; the last n - 1 projected rows of a request live in its state slot), v_from_k (bool: there is no value
-    projection; a key head as it stands before the rotation is also the value head, so the value size is the head size).
+    projection; a key head as it stands before the rotation is also the value head, so the value size is the head size),
+    gate (bool: the heads' outputs, side by side, are multiplied element by element with sigmoid(W_g h), W_g the tensor
+    "g" [n_heads * v_head_dim, hidden], before the output projection; with the 32-bit head preparation only), o_bias
+    "required" (an output bias the file must carry, with the 32-bit head preparation).
 
     Shapes and variants the specialised kernels do not take (a value size of its own, a sink, a rotation of interleaved
     pairs or with a magnitude, a head size that is no multiple of 16) run on the general pair of kernels
@@ -45,7 +48,7 @@ class AttentionMixer(Part):
     NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
              "o": "self_attn.out_proj.weight", "q_norm": "self_attn.q_layernorm.weight",
              "k_norm": "self_attn.k_layernorm.weight", "q_bias": "self_attn.q_proj.bias", "k_bias": "self_attn.k_proj.bias",
-             "v_bias": "self_attn.v_proj.bias", "o_bias": "self_attn.out_proj.bias"}
+             "v_bias": "self_attn.v_proj.bias", "o_bias": "self_attn.out_proj.bias", "g": "self_attn.gate.weight"}
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -77,13 +80,15 @@ class AttentionMixer(Part):
         self.bias_required = p.get("bias") == "required"
         self.qk_conv = dict(p["qk_conv"]) if p.get("qk_conv") else None
         self.v_from_k = bool(p.get("v_from_k", False))
+        self.gate = bool(p.get("gate", False))
+        self.o_bias_required = p.get("o_bias") == "required"
         if self.v_from_k and (self.vd != self.hd or self.v_share is not None):
             raise ValueError("attention: keys that are their own values need value size = head size and no shared values")
         if self.qk_conv is not None and not 1 <= int(self.qk_conv["taps"]) <= 17:
             raise ValueError(f"attention: {self.qk_conv['taps']} conv taps are not supported by the kernel (1 to 17)")
         # whole heads in 32-bit before anything is rounded: biases, convolution, rotation, the norm without a weight, shared values
         self.prepared = (self.unit_norm or self.v_share is not None or self.bias_required or self.qk_conv is not None
-                         or self.v_from_k)
+                         or self.v_from_k or self.gate or self.o_bias_required)
         self.general = (self.sink or self.vd != self.hd or self.hd % 16 != 0 or self.position.interleaved
                         or self.position.magnitude != 1.0 or self.prepared or self.softcap > 0.0)
         if self.prepared and (self.qk_norm or self.position.interleaved or self.position.magnitude != 1.0):
@@ -120,12 +125,17 @@ class AttentionMixer(Part):
                       WeightSpec(n["o_bias"], ((H,),), role="vector", init=("bias",), optional=True)]
         if self.v_share is not None:
             specs.append(WeightSpec(self.prefix + self.v_share["lambda"], ((),), role="vector", init=("uniform", 0.2, 0.8)))
+        if self.gate:
+            specs.append(WeightSpec(n["g"], ((self.nh * vd, H),)))
+        if self.o_bias_required:
+            specs.append(WeightSpec(n["o_bias"], ((H,),), role="vector", init=("bias",)))
         return specs + self.position.weight_specs()
 
     def bind(self, tensors):
         n = self.names
         # one fused projection [q | k | v]: a layout choice, the arithmetic is unchanged
-        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]]] + ([] if self.v_from_k else [tensors[n["v"]]]), dim=0).contiguous()
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]]] + ([] if self.v_from_k else [tensors[n["v"]]])
+                               + ([tensors[n["g"]]] if self.gate else []), dim=0).contiguous()
         if self.qk_conv is not None:
             self.conv_w = torch.cat([tensors[self.prefix + self.qk_conv["q"]], tensors[self.prefix + self.qk_conv["k"]]], dim=0).contiguous()
         self.w_o = tensors[n["o"]]
@@ -142,6 +152,8 @@ class AttentionMixer(Part):
                 self.b_qkv = torch.cat([t.float() if t is not None else torch.zeros(w, dtype=torch.float32, device=ref.device)
                                         for t, w in parts]).contiguous()
             self.b_o = tensors.get(n["o_bias"])
+        if self.o_bias_required:
+            self.b_o = tensors[n["o_bias"]]
         self.position.bind(tensors)
 
     def cache_specs(self):
@@ -185,8 +197,12 @@ class AttentionMixer(Part):
             if not kv.writes:
                 raise ValueError("attention: a layer that reads another entry's cache cannot prepare heads in 32-bit")
             # the product in 32-bit, so that biases, angles and the norm without a weight see unrounded heads
-            qkv = rt.workspace.get("attn_qkv32", (T, width), torch.float32, first="tokens")
-            ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+            wide = width + (nh * vd if self.gate else 0)          # the gate's pre-activations ride along, unrounded
+            qkv = rt.workspace.get("attn_qkv32", (T, wide), torch.float32, first="tokens")
+            ops.linear(x, self.w_qkv[:wide], qkv, status=rt.status)
+            gate = qkv[:, width:] if self.gate else None
+            if self.gate:
+                qkv = qkv[:, :width]
             bias = self.b_qkv
             if self.qk_conv is not None:
                 # the convolution reads the biased product (the bias is the projection's) and leaves plain 32-bit rows
@@ -247,7 +263,11 @@ class AttentionMixer(Part):
         if not done:
             ops.attention_any(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, self.window,
                               self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status, softcap=self.softcap)
+        if self.prepared and self.gate:
+            ops.sigmoid_gate(out, gate)
         ops.linear(out, self.w_o, residual, accumulate=accumulate, status=rt.status)
+        if self.prepared and self.b_o is not None:
+            ops.add_bias(residual, self.b_o)
 
     def forward(self, x, batch, caches, residual, accumulate=True, projected=None):
         kv = caches[0]

@@ -126,6 +126,8 @@ class ParallelResidualBlock(Block):
         import inspect
         self._one_pass = (self.ff is not None and hasattr(self.ff, "forward_into")
                           and "extra" in inspect.signature(self.mixer.forward).parameters)
+        # a feed-forward whose forward() has an `accumulate` keyword may default to overwriting: here it adds
+        self._ff_adds = self.ff is not None and "accumulate" in inspect.signature(self.ff.forward).parameters
 
     def weight_specs(self):
         return [w for p in self.parts for w in p.weight_specs()]
@@ -192,6 +194,8 @@ class ParallelResidualBlock(Block):
         if probe:
             probe("stream_mixer", x)
         if self.ff is not None:
+            if self._ff_adds:
+                kw["accumulate"] = True
             self.ff.forward(h, batch, x, **kw)
         ops.settle(x)
         if probe:

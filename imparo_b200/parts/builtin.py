@@ -8,6 +8,7 @@ from .feedforward import DenseFeedForward, SwiGLU
 from .latent_attention import LatentAttention
 from .linear_attention import DecayLinearAttention
 from .mamba2 import Mamba2Mixer
+from .mlstm import MatrixMemory
 from .moe import RoutedExperts
 from .norm import RMSNorm
 from .position import NoPosition, RotaryInterleaved, RotaryNeox
@@ -36,3 +37,4 @@ register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
 register_part("block", "hyper_connections", HyperConnectionBlock, replace=True)
 register_part("mixer", "latent_attention", LatentAttention, replace=True)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule, replace=True)
+register_part("mixer", "matrix_memory", MatrixMemory, replace=True)

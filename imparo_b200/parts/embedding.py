@@ -15,7 +15,9 @@ from .spec import WeightSpec
 
 class TokenEmbedding(Part):
     """params: vocab, width, name, scale (optional factor on the rows, applied in 32-bit), copies (optional n > 1: the
-    stream holds n copies of every row side by side, [tokens, n * width], for arrangements that keep several)."""
+    stream holds n copies of every row side by side, [tokens, n * width], for arrangements that keep several), positions
+    (optional {"name": tensor, "rows": n}: a learned vector per position, [n, width], added unscaled to the scaled row; a
+    token at a position beyond the table is reported through the status word)."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -24,20 +26,29 @@ class TokenEmbedding(Part):
         self.name = prefix + params["name"]
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
         self.copies = int(params.get("copies") or 1)
-        self.table = None
+        pos = params.get("positions")
+        self.pos_name = prefix + pos["name"] if pos else None
+        self.pos_rows = int(pos["rows"]) if pos else 0
+        self.table = self.pos_table = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, ((self.vocab, self.width),))]
+        specs = [WeightSpec(self.name, ((self.vocab, self.width),))]
+        if self.pos_name is not None:
+            specs.append(WeightSpec(self.pos_name, ((self.pos_rows, self.width),)))
+        return specs
 
     def bind(self, tensors):
         self.table = tensors[self.name]
+        if self.pos_name is not None:
+            self.pos_table = tensors[self.pos_name].contiguous()
 
     def forward(self, batch) -> torch.Tensor:
         """batch: the step's batch (token_ids, positions, item_of_token, ... on the device).  This part reads
         the token ids only; an embedding that adds learned positions or segment rows reads the rest."""
         out = self.rt.workspace.get("residual", (batch.n_tokens, self.copies * self.width), torch.float32, first="tokens")
-        if self.scale != 1.0 or self.copies != 1:
-            ops.embed_copies(self.table, batch.token_ids, out, self.rt.status, scale=self.scale, copies=self.copies)
+        if self.scale != 1.0 or self.copies != 1 or self.pos_table is not None:
+            ops.embed_copies(self.table, batch.token_ids, out, self.rt.status, scale=self.scale, copies=self.copies,
+                             pos_table=self.pos_table, positions=batch.positions if self.pos_table is not None else None)
         else:
             ops.embed_gather(self.table, batch.token_ids, out, self.rt.status)
         return out

@@ -11,36 +11,58 @@ from .spec import WeightSpec
 
 
 class SwiGLU(Part):
-    """params: hidden, ff, names (optional).  forward(..., accumulate=False) overwrites `residual` (then any float32
-    [tokens, hidden] buffer) instead of adding into it."""
+    """The gated feed-forward down(act(gate(x)) * up(x)).  params: hidden, ff, names (optional), act ("silu" by default, or
+    "gelu_tanh"), bias (bool, default False: True declares a bias for each of the three products, names "gate_bias",
+    "up_bias", "down_bias"; they are 32-bit and added to the products' results before the activation / after the down
+    product).  forward(..., accumulate=False) overwrites `residual` (then any float32 [tokens, hidden] buffer) instead of
+    adding into it."""
     adds_with_linear = True
 
 
-    NAMES = {"gate": "feed_forward.w1.weight", "up": "feed_forward.w3.weight", "down": "feed_forward.w2.weight"}
+    NAMES = {"gate": "feed_forward.w1.weight", "up": "feed_forward.w3.weight", "down": "feed_forward.w2.weight",
+             "gate_bias": "feed_forward.w1.bias", "up_bias": "feed_forward.w3.bias", "down_bias": "feed_forward.w2.bias"}
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.hidden = int(params["hidden"])
         self.ff = int(params["ff"])
+        self.act = params.get("act", "silu")
+        if self.act not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: unknown activation '{self.act}' (silu, gelu_tanh)")
+        self.bias = bool(params.get("bias", False))
         self.names = {k: prefix + v for k, v in {**self.NAMES, **params.get("names", {})}.items()}
-        self.w_gu = self.w_down = None
+        self.w_gu = self.w_down = self.b_gu = self.b_down = None
 
     def weight_specs(self):
         n, H, F = self.names, self.hidden, self.ff
-        return [WeightSpec(n["gate"], ((F, H),)), WeightSpec(n["up"], ((F, H),)), WeightSpec(n["down"], ((H, F),))]
+        specs = [WeightSpec(n["gate"], ((F, H),)), WeightSpec(n["up"], ((F, H),)), WeightSpec(n["down"], ((H, F),))]
+        if self.bias:
+            specs += [WeightSpec(n["gate_bias"], ((F,),), role="vector", init=("bias",)),
+                      WeightSpec(n["up_bias"], ((F,),), role="vector", init=("bias",)),
+                      WeightSpec(n["down_bias"], ((H,),), role="vector", init=("bias",))]
+        return specs
 
     def bind(self, tensors):
         n = self.names
         # one fused projection [gate | up]
         self.w_gu = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
         self.w_down = tensors[n["down"]]
+        if self.bias:
+            self.b_gu = torch.cat([tensors[n["gate_bias"]].float(), tensors[n["up_bias"]].float()]).contiguous()
+            self.b_down = tensors[n["down_bias"]]
 
     def forward(self, x, batch, residual, accumulate=True):
         rt, T, F = self.rt, x.shape[0], self.ff
         h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype, first="tokens")
-        # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
-        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
+        if self.act == "silu" and not self.bias:
+            # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
+            ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
+        else:
+            ops.linear_gated(x, self.w_gu, h, self.act, bias=self.b_gu, status=rt.status,
+                             tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
         ops.linear(h, self.w_down, residual, accumulate=accumulate, status=rt.status)
+        if self.b_down is not None:
+            ops.add_bias(residual, self.b_down)
 
 
 class DenseFeedForward(Part):

@@ -7,6 +7,9 @@ mean of the branches' outputs, each first RMS-normed over the model width with a
 
 added into the stream times `scale` (the arrangement's residual factor).  The branches write 32-bit buffers
 [tokens, hidden]; the norms, the mean and the add are one kernel.
+
+With `weights` (a factor per branch) the result is instead the plain weighted sum  out = sum_b weights[b] * branch_b(x),
+without norms (no norm tensors are read); the sum and the add are one kernel.
 """
 from __future__ import annotations
 
@@ -19,16 +22,22 @@ from .spec import WeightSpec
 
 class SideBySideMixer(Part):
     """params: hidden, eps, branches: a sequence of (sub-prefix, PartSpec of a mixer, name of its output-norm weight
-    after this part's prefix)."""
+    after this part's prefix; None with `weights`), weights (optional: a factor per branch; the branches' outputs are then
+    summed with these factors and not normed)."""
     takes_scale = True
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.hidden = int(params["hidden"])
-        self.eps = float(params["eps"])
+        self.eps = float(params.get("eps", 0.0))
+        self.weights = tuple(float(w) for w in params["weights"]) if params.get("weights") is not None else None
         self.branches = []
         for sub, spec, norm_name in params["branches"]:
-            self.branches.append((make_part("mixer", spec, prefix + sub, rt), prefix + norm_name))
+            self.branches.append((make_part("mixer", spec, prefix + sub, rt), prefix + norm_name if norm_name else None))
+        if self.weights is not None and len(self.weights) != len(self.branches):
+            raise ValueError("side-by-side mixer: one weight per branch")
+        if self.weights is None and any(n is None for _, n in self.branches):
+            raise ValueError("side-by-side mixer: every branch needs its output-norm weight (or the mixer its `weights`)")
         if not 1 <= len(self.branches) <= 4:
             raise ValueError("side-by-side mixer: one to four branches")
         self.graph_safe = all(b.graph_safe for b, _ in self.branches)
@@ -39,14 +48,16 @@ class SideBySideMixer(Part):
         specs = []
         for b, norm_name in self.branches:
             specs += b.weight_specs()
-            specs.append(WeightSpec(norm_name, ((self.hidden,),), role="vector", init=("norm",)))
+            if self.weights is None:
+                specs.append(WeightSpec(norm_name, ((self.hidden,),), role="vector", init=("norm",)))
         return specs
 
     def bind(self, tensors):
         self.norm_w = []
         for b, norm_name in self.branches:
             b.bind(tensors)
-            self.norm_w.append(tensors[norm_name])
+            if self.weights is None:
+                self.norm_w.append(tensors[norm_name])
 
     def cache_specs(self):
         return tuple(s for b, _ in self.branches for s in b.cache_specs())
@@ -91,5 +102,14 @@ class SideBySideMixer(Part):
             b.forward(x, batch, caches[at:at + self._n_caches[i]], buf, accumulate=False, **kw)
             at += self._n_caches[i]
             outs.append(buf)
+        if self.weights is not None:
+            ys, cs = list(outs), [scale * w for w in self.weights]
+            if extra is not None:
+                ys.append(extra)
+                cs.append(extra_scale)
+            ops.add_weighted(residual, ys[:4], cs[:4])
+            if len(ys) > 4:
+                ops.add_weighted(residual, ys[4:], cs[4:])
+            return
         # (the add may stay pending for the next norm of the stream to carry out: ops.allow_deferred_add by the arrangement)
         ops.norm_mean_add(residual, outs, self.norm_w, self.eps, scale / len(outs), extra, extra_scale, defer=True)
