@@ -22,7 +22,7 @@ continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 3
 print one JSON line each; --workload sizes runs the headline's model at further prompt lengths
 and decode contexts; --workload vipotar / negotar run the Vipotar / Negotar design at two sizes that resemble a real model's layers beside
 LFM2 at equal width, depth, heads and feed-forward size (prefill of one prompt, decode at batch 8), --workload keralix the
-Keralix design beside Vipotar likewise; the default is the headline above.
+Keralix design beside Vipotar likewise, --workload zepesun the Zepesun design beside Negotar; the default is the headline above.
 """
 import argparse
 import json
@@ -529,6 +529,121 @@ def workload_keralix(args):
     return 0
 
 
+def zepesun_config(width, layers, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank, heads, kv_heads, head, window, mem_heads,
+                   mem_dim, mem_vdim, experts, top, groups, keep, ff, vocab, positions):
+    """A Zepesun config.json of the given sizes: layers in the order latent attention, parallel (windowed attention beside a
+    matrix memory), matrix memory, matrix memory, and so on; the first layer with a dense feed-forward of top * ff features,
+    the others routed (`experts` clamped experts of `ff` features in `groups` groups of which `keep` are candidates, `top` per
+    token, and a shared one)."""
+    lat = {"heads": lat_heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": lat_vdim, "kv_rank": kv_rank,
+           "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 250000.0, "dims": rot_dim}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "mask": {"size": window}}
+    mem = {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": 15.0}
+    par = {"left": left, "right": mem, "left_scale": 1.2, "right_scale": 0.5}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}},
+           "expert": {"ff": ff, "limit": 1.0}, "shared": {"ff": ff, "limit": 1.0}}
+    kinds = [("latent_attention", lat), ("parallel", par), ("mlstm", mem), ("mlstm", mem)]
+    return {"architecture": "Zepesun", "vocab": vocab, "width": width, "max_positions": positions, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 3.0},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": top * ff} if i == 0 else moe}
+                       for i in range(layers)]}
+
+
+def workload_zepesun(args):
+    """Zepesun at two sizes beside Negotar (attention and a gated recurrent mixer in turn, a routed feed-forward: the closest
+    design the engine serves) at equal width, depth, attention heads, experts and expert size: prefill of one prompt of 512
+    and 2,048 tokens, decode steps of 8 requests with 2,048 positions each.  Rooflines: prefill against the measured
+    bfloat16 peak with the flops the design needs (products over all tokens, the experts a token uses and the shared one,
+    attention over the window, the latent attention in its latent space over all earlier positions, the matrix memory's
+    4 * heads * dim * vdim per token); decode against the measured copy bandwidth with the bytes a step must move (every
+    dense matrix once, the experts the step's rows can reach at most and the shared ones, the windows' keys and values, the
+    cached latent rows, the memories read and written)."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    sizes = {"width1024": dict(width=1024, layers=8, lat_heads=16, lat_dim=64, rot_dim=32, lat_vdim=64, kv_rank=96, heads=16, kv_heads=4,
+                               head=64, window=512, mem_heads=8, mem_dim=64, mem_vdim=128, experts=16, top=2, groups=4, keep=2, ff=1024,
+                               vocab=32768, positions=CTX),
+             "width2048": dict(width=2048, layers=8, lat_heads=32, lat_dim=64, rot_dim=32, lat_vdim=64, kv_rank=96, heads=32, kv_heads=8,
+                               head=64, window=1024, mem_heads=16, mem_dim=128, mem_vdim=128, experts=32, top=4, groups=8, keep=4, ff=1024,
+                               vocab=65536, positions=CTX)}
+    out = {"metric": "Zepesun beside Negotar at equal sizes: prefill of one prompt, decode at batch 8 with 2,048 positions",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name, z in sizes.items():
+            row = {}
+            W, L, V = z["width"], z["layers"], z["vocab"]
+            expert = 3 * W * z["ff"]
+            for model in ("zepesun", "negotar"):
+                if model == "zepesun":
+                    cfg = zepesun_config(**z)
+                    kinds = [cfg["layers"][i]["type"] for i in range(L)]
+                    n_lat, n_par = kinds.count("latent_attention"), kinds.count("parallel")
+                    n_mem = kinds.count("mlstm") + n_par
+                    LH, LD, LR, LV, C = z["lat_heads"], z["lat_dim"], z["rot_dim"], z["lat_vdim"], z["kv_rank"]
+                    H, G, D = z["heads"], z["kv_heads"], z["head"]
+                    MH, MD, MV = z["mem_heads"], z["mem_dim"], z["mem_vdim"]
+                    lat = (LH * (LD + LR) + C + LR + LH) * W + LH * LD * C + LH * LV * C + W * LH * LV
+                    left = (2 * H * D + 2 * G * D) * W + W * H * D
+                    mem = (2 * MH * MD + 2 * MH * MV + 2 * MH) * W + W * MH * MV
+                    dense = n_lat * lat + n_par * left + n_mem * mem + (L - 1) * z["experts"] * W + z["top"] * expert
+                    state = n_mem * MH * (MD * MV + MD) * 4
+
+                    def flops(T):
+                        keys = sum(min(t + 1, z["window"]) for t in range(T))
+                        return (2.0 * T * (dense + (L - 1) * (z["top"] + 1) * expert) + 2.0 * V * W + n_par * 4.0 * H * D * keys
+                                + n_lat * 2.0 * LH * (2 * C + LR) * T * (T + 1) / 2 + n_mem * 4.0 * MH * MD * MV * T)
+
+                    def step_bytes(batch, ctx):
+                        reached = min(z["experts"], batch * z["top"]) + 1
+                        per_request = 2 * state + n_par * min(ctx, z["window"]) * 2 * G * D * 2 + n_lat * ctx * (C + LR) * 2
+                        return (dense + (L - 1) * reached * expert + V * W) * 2 + batch * per_request
+                    params = dense + (L - 1) * (z["experts"] + 1) * expert + 2 * V * W + z["positions"] * W
+                else:
+                    n = dict(width=W, layers=L, heads=z["heads"], kv_heads=z["kv_heads"], head=z["head"], ssm_heads=z["mem_heads"] * 2,
+                             ssm_vdim=z["mem_vdim"] // 2, ssm_state=z["mem_dim"], experts=z["experts"], top=z["top"], ff=z["ff"], vocab=V)
+                    cfg = negotar_config(**n)
+                    n_attn = (L + 1) // 2
+                    n_ssm = L - n_attn
+                    inner, N = n["ssm_heads"] * n["ssm_vdim"], n["ssm_state"]
+                    attn = (n["heads"] + 2 * n["kv_heads"]) * n["head"] * W + W * n["heads"] * n["head"]
+                    ssm = (2 * inner + 2 * N + n["ssm_heads"]) * W + W * inner
+                    dense = n_attn * attn + n_ssm * ssm + L * n["experts"] * W
+                    state = n_ssm * n["ssm_heads"] * N * n["ssm_vdim"] * 4
+                    kv_tok = n_attn * 2 * n["kv_heads"] * n["head"] * 2
+                    params = dense + L * n["experts"] * expert + V * W
+
+                    def flops(T):
+                        return (2.0 * T * (dense + L * n["top"] * expert) + 2.0 * V * W
+                                + n_attn * 4.0 * n["heads"] * n["head"] * T * (T + 1) / 2 + n_ssm * 6.0 * inner * N * T)
+
+                    def step_bytes(batch, ctx):
+                        reached = min(n["experts"], batch * n["top"])
+                        return (dense + L * reached * expert + V * W) * 2 + batch * (2 * state + ctx * kv_tok)
+                engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=8, page_size=PAGE, max_step_tokens=PROMPT,
+                                random_init={"norm_jitter": 0.0})
+                r = {"params": params, "prefill": {}}
+                for T in (512, 2048):
+                    ms = measure_prefill(engine, reps=5, warmup=3, rng=rng, prompt=T)
+                    r["prefill"][str(T)] = {"value": round(T * 1000.0 / ms, 1), "ms": round(ms, 3),
+                                            "frac": round(flops(T) / (ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+                ms, launches, library, ctx = measure_decode(engine, 8, max(20, args.steps // 4), max(args.warmup, 3), rng, prompt=PROMPT)
+                nbytes = step_bytes(8, ctx)
+                r["decode_b8"] = {"value": round(8 * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "own_kernels_per_step": round(launches, 1),
+                                  "library_gemms_per_step": round(library, 1), "bytes_per_step": int(nbytes),
+                                  "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                row[model] = r
+                del engine
+                torch.cuda.empty_cache()
+            out["sizes"][name] = dict(row, config=z)
+    out["peaks"] = pk["source"]
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def _preset(name):
     with open(os.path.join(ROOT, "imparo_b200", "config", "presets", name + ".json")) as f:
         return json.load(f)
@@ -747,7 +862,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar", "keralix"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar", "keralix", "zepesun"],
                     help="headline (default): the one JSON line described at the top of this file.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit.  "
@@ -779,6 +894,8 @@ def main():
         return workload_negotar(args)
     if args.workload == "keralix":
         return workload_keralix(args)
+    if args.workload == "zepesun":
+        return workload_zepesun(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

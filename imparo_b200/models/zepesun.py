@@ -74,7 +74,7 @@ def zepesun_model_spec(cfg: ZepesunConfig) -> ModelSpec:
     return ModelSpec(
         architecture="Zepesun", vocab_size=cfg.vocab, hidden_size=W,
         embedding=PartSpec("token_table", {"vocab": cfg.vocab, "width": W, "name": "embed", "scale": cfg.embedding_scale,
-                                           "positions": positions}),
+                                           "position_table": positions}),
         layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
         final_norm=PartSpec("rmsnorm", {"width": W, "eps": cfg.eps, "name": "final.norm"}),
         head=PartSpec("linear", {"vocab": cfg.vocab, "width": W, "name": "head"}),

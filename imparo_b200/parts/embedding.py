@@ -15,7 +15,7 @@ from .spec import WeightSpec
 
 class TokenEmbedding(Part):
     """params: vocab, width, name, scale (optional factor on the rows, applied in 32-bit), copies (optional n > 1: the
-    stream holds n copies of every row side by side, [tokens, n * width], for arrangements that keep several), positions
+    stream holds n copies of every row side by side, [tokens, n * width], for arrangements that keep several), position_table
     (optional {"name": tensor, "rows": n}: a learned vector per position, [n, width], added unscaled to the scaled row; a
     token at a position beyond the table is reported through the status word)."""
 
@@ -26,7 +26,7 @@ class TokenEmbedding(Part):
         self.name = prefix + params["name"]
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
         self.copies = int(params.get("copies") or 1)
-        pos = params.get("positions")
+        pos = params.get("position_table")
         self.pos_name = prefix + pos["name"] if pos else None
         self.pos_rows = int(pos["rows"]) if pos else 0
         self.table = self.pos_table = None

@@ -117,7 +117,8 @@ def latent_attention(h, W, p, m, eps, positions):
 
 def window_attention(h, W, p, m):
     T = h.shape[0]
-    H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    H, D = int(m["heads"]), int(m["dim"])
+    G, V = int(m.get("kv_heads", H)), int(m.get("vdim", D))
     q = (h @ W[p + "q"].T + W[p + "q.b"]).reshape(T, H, D)
     k = (h @ W[p + "k"].T + W[p + "k.b"]).reshape(T, G, D)
     v = (h @ W[p + "v"].T + W[p + "v.b"]).reshape(T, G, V)
@@ -188,32 +189,43 @@ def clamped_expert(h, W, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
-def route(z, top, groups, keep, scale):
-    """z [T, E] router logits -> (ids [T, top], weights [T, top])."""
+def route(z, top, groups, keep, scale, gaps=None):
+    """z [T, E] router logits -> (ids [T, top], weights [T, top]).  gaps: a list that receives, per row, how far (in logits)
+    the closest decision was from going the other way: the last kept group against the first one left out, the last chosen
+    expert against the best candidate that was not chosen."""
     T, E = z.shape
     s = softmax_rows(z)
     allowed = np.ones_like(s, dtype=bool)
+    gap = np.full(T, np.inf)
     if groups > 1 and keep < groups:
         per = E // groups
         gs = s.reshape(T, groups, per).max(axis=2)
-        order = np.argsort(-gs, axis=1, kind="stable")[:, :keep]
+        order = np.argsort(-gs, axis=1, kind="stable")
         ok = np.zeros((T, groups), dtype=bool)
-        np.put_along_axis(ok, order, True, axis=1)
+        np.put_along_axis(ok, order[:, :keep], True, axis=1)
         allowed = np.repeat(ok, per, axis=1)
+        zg = z.reshape(T, groups, per).max(axis=2)
+        gap = np.take_along_axis(zg, order[:, keep - 1:keep], axis=1)[:, 0] - np.take_along_axis(zg, order[:, keep:keep + 1], axis=1)[:, 0]
     masked = np.where(allowed, s, -1.0)
-    ids = np.argsort(-masked, axis=1, kind="stable")[:, :top]
+    order = np.argsort(-masked, axis=1, kind="stable")
+    ids = order[:, :top]
+    if top < E:
+        zm = np.where(allowed, z, -np.inf)
+        nxt = np.take_along_axis(zm, order[:, top:top + 1], axis=1)[:, 0]
+        gap = np.minimum(gap, np.take_along_axis(zm, order[:, top - 1:top], axis=1)[:, 0] - nxt)
+    if gaps is not None:
+        gaps.append(gap)
     w = np.take_along_axis(s, ids, axis=1)
     w = w / (w.sum(axis=1, keepdims=True) + 1e-20) * scale
     return ids, w
 
 
-def moe_ff(h, W, p, mlp, router_dtype=None):
+def moe_ff(h, W, p, mlp, gaps=None):
     T = h.shape[0]
     r = mlp["router"]
     groups = r.get("groups") or {}
-    hr = h if router_dtype is None else h.astype(router_dtype)
-    z = hr @ W[p + "router"].astype(hr.dtype).T
-    ids, w = route(z, int(r["top"]), int(groups.get("count", 1)), int(groups.get("keep", 1)), float(r.get("scale", 1.0)))
+    z = h @ W[p + "router"].T
+    ids, w = route(z, int(r["top"]), int(groups.get("count", 1)), int(groups.get("keep", 1)), float(r.get("scale", 1.0)), gaps)
     limit = float(mlp["expert"]["limit"])
     out = np.zeros((T, W[p + "e0.down"].shape[0]), dtype=h.dtype)
     for t in range(T):
@@ -229,7 +241,7 @@ def moe_ff(h, W, p, mlp, router_dtype=None):
 # the model
 # ----------------------------------------------------------------------------
 
-def layer_output(x, W, L, p, eps, positions):
+def layer_output(x, W, L, p, eps, positions, gaps=None):
     h = unit_rms(x, eps) * W[p + "norm1"]
     kind, m = L["type"], L["mixer"]
     if kind == "latent_attention":
@@ -242,20 +254,21 @@ def layer_output(x, W, L, p, eps, positions):
         raise ValueError(f"unknown layer type {kind!r}")
     mlp = L.get("mlp")
     if mlp is not None:
-        y = y + (dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, W, p + "mlp.", mlp))
+        y = y + (dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, W, p + "mlp.", mlp, gaps))
     return x + y
 
 
-def forward(cfg, W, tokens, dtype=np.float64, layer_outputs=None):
+def forward(cfg, W, tokens, dtype=np.float64, layer_outputs=None, gaps=None):
     """cfg: the config.json dictionary; W: name -> array; tokens: one sequence.  Returns logits [T, vocab].
-    layer_outputs: a list that receives the stream after every layer."""
+    layer_outputs: a list that receives the stream after every layer; gaps: a list that receives every routed layer's
+    per-row decision gaps (route)."""
     W = {k: np.asarray(v, dtype=dtype) for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     tokens = np.asarray(tokens)
     positions = np.arange(len(tokens))
     x = W["embed"][tokens] * dtype((cfg.get("embedding") or {}).get("scale", 1.0)) + W["pos"][positions]
     for i, L in enumerate(cfg["layers"]):
-        x = layer_output(x, W, L, f"l{i}.", eps, positions)
+        x = layer_output(x, W, L, f"l{i}.", eps, positions, gaps)
         if layer_outputs is not None:
             layer_outputs.append(x)
     x = unit_rms(x, eps) * W["final.norm"]

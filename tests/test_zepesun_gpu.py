@@ -1,0 +1,696 @@
+"""Zepesun on the GPU against the plain implementation (tests/plain/zepesun_plain.py), in 32-bit and bfloat16:
+each mechanism's kernel alone, the replay families (whole, last tokens one by one, portions down to two tokens, mixed
+batches with pages and slots used again), a marked key just inside and just outside the window at page borders, a far
+position found through the latent and through the rotated key part, a far token carried by the matrix memory, the first
+tokens of a sequence, long decoding, long portions, and greedy generation through Engine.generate, the command line and
+bin/trace_run."""
+import functools
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+from tests import traces
+from tests import zepesun_cases as C
+from tests.plain import zepesun_plain as P
+from tests.plain.lfm2_plain import read_safetensors
+from tests.zepesun_configs import ALL, PAGE
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# Fractions of the largest |logit| of the compared requests.  float32 is the sharp test.  bfloat16: nine places in ten stay
+# within TOL and none leaves WORST (a wrong key, state, window or expert moves a place by the scale itself).
+TOL = {"float32": 3e-5, "bfloat16": 3e-2}
+WORST = {"float32": 3e-5, "bfloat16": 0.15}
+_tmp = tempfile.TemporaryDirectory(prefix="imparo_b200_zepesun_")
+
+
+def rescale(path):
+    """The drawn matrices are small, and then every token looks alike to the layers.  Matrices are scaled to a standard
+    deviation of 1 / sqrt(columns) (the embedding to 1, position vectors to 0.5), so that tokens, positions, projections,
+    biases, gates and routers all weigh in."""
+    import torch
+    from imparo_b200.weights.safetensors_io import write_safetensors
+    out = {}
+    for k, v in read_safetensors(path).items():
+        t = torch.as_tensor(np.asarray(v))
+        if v.ndim == 2:
+            std = {"embed": 1.0, "pos": 0.5}.get(k, 1.0 / np.sqrt(v.shape[1]))
+            t = (t.float() / t.float().std() * std).to(t.dtype)
+        elif k.endswith(".b") and not k.endswith((".i.b", ".f.b")):
+            t = t * 10.0
+        out[k] = t
+    write_safetensors(path, out)
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(name, seed=1):
+    from imparo_b200.weights import write_random_model
+    d = os.path.join(_tmp.name, f"{name}_{seed}")
+    write_random_model(d, ALL[name], seed=seed, dtype="bfloat16", norm_jitter=0.3)
+    rescale(os.path.join(d, "model.safetensors"))
+    return d
+
+
+@functools.lru_cache(maxsize=None)
+def weights(name, seed=1):
+    return read_safetensors(os.path.join(model_dir(name, seed), "model.safetensors"))
+
+
+def make_requests(name, lengths, seed=0):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, ALL[name]["vocab"], n).tolist() for i, n in enumerate(lengths)}
+
+
+_plain, _gaps = {}, {}
+CLOSE_CALL = 0.03          # router decisions closer than this (in logits) may go the other way under 8-bit rounding
+AFTER = 3                  # and the mixers carry such a place's deviation on to the next few
+
+
+def plain_logits(name, requests, seed=1):
+    out = {}
+    for rid, toks in requests.items():
+        key = (name, seed, tuple(toks))
+        if key not in _plain:
+            gaps = []
+            _plain[key] = P.forward(ALL[name], weights(name, seed), toks, gaps=gaps)
+            _gaps[key] = np.min(np.stack(gaps), axis=0) if gaps else np.full(len(toks), np.inf)
+        out[rid] = _plain[key]
+    return out
+
+
+def close_calls(name, requests, seed=1):
+    """(request, position) places at which a router decision of the plain implementation was a close call, and the places
+    right after each: bfloat16 may decide them the other way, and another expert's output is another vector altogether."""
+    plain_logits(name, requests, seed)
+    out = set()
+    for rid, toks in requests.items():
+        for p in np.nonzero(_gaps[(name, seed, tuple(toks))] < CLOSE_CALL)[0]:
+            out.update((rid, int(p) + k) for k in range(AFTER + 1))
+    return out
+
+
+def engine_for(name, dtype, steps, parallel=4, page=None, **kw):
+    from imparo_b200.engine import Engine
+    page = page or PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, max(64, page))
+    return Engine(model_dir(name), dtype=dtype, ctx=max_tokens, parallel=parallel, page_size=page,
+                  num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens), **kw)
+
+
+def all_errors(steps, got, want):
+    at, out = {}, []
+    for s in steps:
+        r = 0
+        for e in s["entries"]:
+            start = at.get(e["id"], 0)
+            for w in e["want"]:
+                out.append((s["step"], e["id"], start + w, float(np.abs(got[s["step"]][r] - want[s["step"]][r]).max())))
+                r += 1
+            at[e["id"]] = start + len(e["tokens"])
+        for name in s["end"]:
+            at.pop(name, None)
+    return out
+
+
+def check_trace(engine, steps, name, requests, dtype, share=0.1):
+    from tests.gpu_helpers import run_trace
+    ref = plain_logits(name, requests)
+    want = traces.expected(steps, ref)
+    got = run_trace(engine, steps)
+    assert sorted(got) == sorted(want)
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    errs = all_errors(steps, got, want)
+    if dtype == "bfloat16":
+        skip = close_calls(name, requests)
+        kept = [e for e in errs if (e[1], e[2]) not in skip]
+        assert len(kept) >= 0.5 * len(errs), "more than half of the places are close calls of a router"
+        errs = kept
+    bad = next((e for e in errs if not e[3] <= WORST[dtype] * scale), None)
+    assert bad is None, (f"first wrong place: step {bad[0]}, request {bad[1]}, position {bad[2]}, "
+                         f"error {bad[3]:.3e} > {WORST[dtype] * scale:.3e}")
+    over = [e for e in errs if not e[3] <= TOL[dtype] * scale]
+    assert len(over) <= share * len(errs), f"{len(over)} of {len(errs)} places beyond {TOL[dtype] * scale:.3e}; the first: {over[0]}"
+    assert engine.cache.n_requests() == 0
+    return got
+
+
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51], "B": [5, 23, 140, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [150, 47, 96, 201, 64],
+           "E": [60, 75, 40, 104, 52, 83]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ALL))
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_family(name, dtype, family):
+    reqs = make_requests(name, LENGTHS[name])
+    steps = {"whole": traces.whole, "tail": lambda r: traces.tail_one_by_one(r, tail=44), "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[family](reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    if family == "mixed":
+        assert traces.max_live_tokens(steps) < sum(traces.round_up(len(t), 64) for t in reqs.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_cutting_does_not_change_logits_beyond_rounding(name, dtype):
+    from tests.gpu_helpers import run_trace
+    reqs = make_requests(name, [61, 47, 75], seed=5)
+    outs = []
+    for build in (traces.whole, traces.tail_one_by_one, traces.portions, lambda r: traces.mixed(r, seed=9)):
+        steps = build(reqs)
+        got = run_trace(engine_for(name, dtype, steps), steps)
+        by_pos, at = {}, {}
+        for s in steps:
+            r = 0
+            for e in s["entries"]:
+                start = at.get(e["id"], 0)
+                for w in e["want"]:
+                    by_pos[(e["id"], start + w)] = got[s["step"]][r]
+                    r += 1
+                at[e["id"]] = start + len(e["tokens"])
+        outs.append(by_pos)
+    keys = set(outs[1]) & set(outs[0])
+    assert len(keys) > 90
+    scale = max(float(np.abs(v).max()) for v in outs[0].values())
+    tol = (2e-5 if dtype == "float32" else 0.1) * scale
+    for k in keys:
+        for o in outs[1:]:
+            if k in o:
+                assert np.abs(o[k] - outs[0][k]).max() <= tol, k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+def test_long_portions(name, dtype):
+    """Prompts of several hundred tokens, whole and in portions of 71 to 300 tokens beside another request's single tokens:
+    whole tiles of the tensor-core attention, windows that pass over many pages, the matrix memory in chunks, the experts
+    sorted into tiles."""
+    reqs = make_requests(name, [700, 333], seed=13)
+    steps = traces.whole(reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    a, b = reqs["r0"], reqs["r1"]
+    steps, at_a, at_b = [], 0, 0
+    steps.append({"step": 0, "entries": [{"id": "b", "tokens": b[:300], "want": [0, 150, 299]}], "end": []})
+    at_b = 300
+    for n in (300, 129, 200, 71):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[at_a:at_a + n], "want": [0, n // 2, n - 1]},
+                                                     {"id": "b", "tokens": [b[at_b]], "want": [0]}],
+                      "end": ["a"] if at_a + n == 700 else []})
+        at_a += n
+        at_b += 1
+    steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": b[at_b:], "want": [0, len(b) - at_b - 1]}], "end": ["b"]})
+    check_trace(engine_for(name, dtype, steps), steps, name, {"a": a, "b": b}, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(name, dtype):
+    """390 tokens one by one: the caches grow over many pages, the windows pass, the states are carried through every step."""
+    reqs = make_requests(name, [400], seed=8)
+    steps = traces.tail_one_by_one(reqs, tail=390)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
+def test_first_tokens_of_a_sequence(name, dtype):
+    reqs = make_requests(name, [1, 2, 3, 6], seed=11)
+    for build in (traces.whole, lambda r: traces.tail_one_by_one(r, tail=8)):
+        steps = build(reqs)
+        check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype, share=0.5 if dtype == "bfloat16" else 0.0)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_state_slots_and_pages_start_clean_when_used_again(name):
+    a = make_requests(name, [50], seed=20)
+    b = {"other": make_requests(name, [37], seed=21)["r0"]}
+    steps = traces.whole(a) + [dict(s, step=s["step"] + 1) for s in traces.portions(b, sizes=(1, 2, 3))]
+    eng = engine_for(name, "float32", steps, parallel=1)       # one slot: it must be reused
+    check_trace(eng, steps, name, dict(a, **b), "float32")
+
+
+# ---- each mechanism's kernel alone ------------------------------------------------------------------------------
+
+def _dev(a, dtype=None):
+    import torch
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def _f32(a):
+    import torch
+    return _dev(np.asarray(a, dtype=np.float32), torch.float32)
+
+
+def _bf16_round(a):
+    import torch
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+def _ragged(cut, items):
+    starts = np.concatenate([[0], np.cumsum([cut[i] for i in items])]).astype(np.int32)
+    iot = np.concatenate([np.full(cut[i], k, dtype=np.int32) for k, i in enumerate(items)])
+    return starts, iot
+
+
+def _run_memory(rows, lens, cuts, slots, b_i, b_f, H, D, V, cap, n_slots=6, chunk=0):
+    """rows: per request the product's rows [q | k | v | gate | i | f].  -> (outputs per request [T, H * V], states)"""
+    import torch
+    from imparo_b200.kernels import ops
+    vb = ops.mlstm_value_blocks(V)
+    S = torch.full((n_slots, H, D, V), 7.0, device="cuda")
+    n = torch.full((n_slots, H, vb, D), 7.0, device="cuda")
+    m = torch.full((n_slots, H, vb), 7.0, device="cuda")
+    for t in (S, n, m):
+        t[slots] = 0.0
+    status = ops.new_status("cuda")
+    got, at = [np.zeros((k, H * V)) for k in lens], [0] * len(lens)
+    qk, vv = H * D, H * V
+    for cut in cuts:
+        items = [i for i in range(len(lens)) if cut[i]]
+        starts, iot = _ragged(cut, items)
+        x = _f32(np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in items]))
+        T = len(iot)
+        o = torch.empty(T, vv, device="cuda")
+        scratch = None
+        if chunk:
+            most = T // chunk + len(items)
+            scratch = (torch.empty(most * H * D * V, device="cuda"), torch.empty(most * H * vb * D, device="cuda"),
+                       torch.empty(most * H * vb * 3, device="cuda"))
+        ops.mlstm_scan(x, 0, qk, 2 * qk, 2 * qk + 2 * vv, 2 * qk + 2 * vv + H, _f32(b_i), _f32(b_f), cap, D ** -0.5, S, n, m,
+                       _dev(starts), _dev(np.array([slots[i] for i in items], dtype=np.int32)), len(items), o, H, D, V, status,
+                       chunk=chunk, scratch=scratch)
+        oc = o.cpu().numpy()
+        for k, i in enumerate(items):
+            got[i][at[i]:at[i] + cut[i]] = oc[starts[k]:starts[k + 1]]
+            at[i] += cut[i]
+    ops.read_status(status)
+    return got, (S, n, m)
+
+
+@pytest.mark.parametrize("chunk", [0, 64, 16])
+@pytest.mark.parametrize("H,D,V,cap", [(4, 32, 48, 12.0), (2, 16, 24, 6.0), (3, 8, 40, 10.0), (1, 40, 70, 3.0), (2, 136, 20, 20.0), (1, 7, 5, 2.0),
+                                       (2, 64, 64, 15.0), (1, 200, 33, 8.0)])
+def test_matrix_memory_kernels(H, D, V, cap, chunk):
+    """Capped gates, the running maximum that starts at zero, the recurrence and the read-out on three requests of unequal
+    length: a launch of portions, then their next portions and single tokens from the states the launches before left
+    (slots in no particular order); row by row and in chunks of 64 and of 16 rows; against the plain recurrence on each
+    whole sequence; the final states too."""
+    rng = np.random.default_rng(H * 100 + D)
+    lens = [137, 5, 190]
+    made = [C.memory_inputs(rng, n, H, D, V) for n in lens]
+    b_i, b_f = made[0][1], made[0][2]
+    rows = [r[0] for r in made]
+    slots = [4, 0, 2]
+    got, (S, n, m) = _run_memory(rows, lens, ([120, 2, 131], [16, 1, 2], [1, 1, 1], [0, 1, 56]), slots, b_i, b_f, H, D, V, cap, chunk=chunk)
+    assert float(S[1].min()) == 7.0 and float(m[5].max()) == 7.0 and float(n[3].min()) == 7.0          # other slots untouched
+    for i, r in enumerate(rows):
+        want, (Sw, nw, mw) = C.memory_plain(r, b_i, b_f, H, D, V, cap)
+        assert np.abs(got[i] - want.reshape(lens[i], -1)).max() <= 3e-5 * np.abs(want).max()
+        assert np.abs(S[slots[i]].cpu().numpy() - Sw).max() <= 3e-5 * max(np.abs(Sw).max(), 1e-3)
+        for b in range(n.shape[2]):                       # every block of value columns keeps its own copy of n and m
+            assert np.abs(n[slots[i], :, b].cpu().numpy() - nw).max() <= 3e-5 * max(np.abs(nw).max(), 1e-3)
+            assert np.abs(m[slots[i], :, b].cpu().numpy() - mw).max() <= 1e-5 * max(np.abs(mw).max(), 1.0)
+
+
+@pytest.mark.parametrize("chunk", [0, 64])
+def test_matrix_memory_carries_a_far_token(chunk):
+    """A pair (k, v) written at the first token is read back hundreds of tokens later by queries along k, in a prompt and in
+    single tokens, although every other key is random (tests/zepesun_cases.py: far_memory_case)."""
+    (H, D, V, cap), rows, b_i, b_f, seekers, want = C.far_memory_case(T=420, prompt=400)
+    got, _ = _run_memory([rows], [420], [[400]] + [[1]] * 20, [1], b_i, b_f, H, D, V, cap, n_slots=2, chunk=chunk)
+    # (forget gates within 1e-4 of one: 400 steps of 32-bit rounding add up where nothing decays)
+    assert np.abs(got[0] - want.reshape(420, -1)).max() <= 3e-4 * np.abs(want).max()
+    assert all(got[0][t, 0] > 4.9 for t in seekers)
+
+
+def _latent_by_kernels(dtype, m, eps, proj, W, cuts, page, tensor_cores=False):
+    """The latent kernels on one request cut as `cuts`; proj: the 32-bit product [T, q | latent | key part | gate]."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    H, D, R, V, Cr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    row = Cr + R
+    T = len(proj)
+    n_blocks = -(-T // page)
+    n_pages = n_blocks + 3
+    table = torch.arange(n_pages - 1, n_pages - 1 - n_blocks, -1, dtype=torch.int32, device="cuda").reshape(1, -1)
+    cache = torch.zeros(n_pages * page * row, dtype=tdt, device="cuda")
+    status = ops.new_status("cuda")
+    w_ukT = _dev(W["uk"].reshape(H, D, Cr).transpose(0, 2, 1), tdt)
+    w_uv = _dev(W["uv"].reshape(H, V, Cr), tdt)
+    n_rot = m["rot"]["dims"] if R and m.get("rot") else 0
+    inv_freq = _f32([float(m["rot"]["base"]) ** (-2.0 * i / n_rot) for i in range(n_rot // 2)]) if n_rot else None
+    out_all, at = np.zeros((T, H * V)), 0
+    gate_off = H * (D + R) + row
+    for n in cuts:
+        pos, iot = _dev(np.arange(at, at + n, dtype=np.int32)), _dev(np.zeros(n, dtype=np.int32))
+        p = _f32(proj[at:at + n])
+        q = torch.empty(n, H * D, dtype=tdt, device="cuda")
+        ql = torch.full((n, H * row), 3.0, dtype=tdt, device="cuda")
+        ops.latent_rot_store(p, H, D, R, Cr, _f32(W["dkv.norm"]), eps, inv_freq, n_rot, pos, iot, q, ql, cache, table, page, n_pages, status)
+        ops.heads_linear(q, w_ukT, ql, out_head=row)
+        ol = torch.empty(n, H * row, dtype=tdt, device="cuda")
+        if not tensor_cores:
+            ops.attention_any(ql, cache, cache, pos, iot, table, page, n_pages, None, m["scale"], False, ol, H, 1, row, row, status)
+        elif n >= 8 and page in (16, 32, 64, 128):
+            assert ops.attention_prefill(ql, cache, cache, _dev(np.array([0, n], dtype=np.int32)), _dev(np.array([at], dtype=np.int32)), 1,
+                                         table, page, n_pages, None, m["scale"], ol, H, 1, row, status, max_group=128)
+        else:
+            chunk, n_splits = ops.split_plan(n, ops.head_groups(H, 1), table.shape[1] * page)
+            part_acc = torch.empty(n * H * n_splits * row, device="cuda")
+            part_ml = torch.empty(n * H * n_splits * 2, device="cuda")
+            assert ops.paged_attention_split_shared(ql, cache, cache, pos, iot, table, page, n_pages, None, m["scale"], ol, part_acc,
+                                                    part_ml, chunk, n_splits, H, 1, row, status)
+        o = torch.empty(n, H * V, dtype=tdt, device="cuda")
+        ops.heads_linear(ol, w_uv, o, gate=p[:, gate_off:gate_off + H], x_head=row)
+        out_all[at:at + n] = o.float().cpu().numpy()
+        at += n
+    ops.read_status(status)
+    return out_all
+
+
+def _latent_weights(rng, m, dtype):
+    H, D, V, Cr = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+    W = {"uk": rng.standard_normal((H * D, Cr)) / np.sqrt(Cr), "uv": rng.standard_normal((H * V, Cr)) / np.sqrt(Cr),
+         "dkv.norm": rng.uniform(0.5, 1.5, Cr)}
+    if dtype == "bfloat16":
+        W.update({k: _bf16_round(W[k]) for k in ("uk", "uv")})
+    return W
+
+
+def _latent_sizes(H, D, R, V, Cr, n_rot=None):
+    m = {"heads": H, "dim": D, "rot_dim": R, "vdim": V, "kv_rank": Cr, "scale": 0.4}
+    if R:
+        m["rot"] = {"base": 300.0, "dims": R if n_rot is None else n_rot}
+    return m
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,D,R,V,Cr,n_rot", [(3, 16, 8, 12, 24, None), (5, 12, 12, 20, 28, 6), (6, 64, 32, 48, 128, None), (2, 24, 4, 8, 260, 2),
+                                              (1, 7, 0, 5, 9, None), (4, 8, 16, 8, 16, 16)])
+def test_latent_attention_kernels(dtype, H, D, R, V, Cr, n_rot):
+    """The latent's norm, the rotation of the shared key part and of the queries' rotated parts, the cache write, queries
+    taken into the latent space, the attention over the cached rows, the way back with a gate per head: a prompt of 45
+    tokens, then 30 tokens one by one (pages of 4)."""
+    rng = np.random.default_rng(H * D + Cr)
+    m = _latent_sizes(H, D, R, V, Cr, n_rot)
+    W = _latent_weights(rng, m, dtype)
+    proj = rng.standard_normal((75, H * (D + R) + Cr + R + H)) * 1.5
+    want = C.latent_rows_plain(m, 1e-5, proj, W)
+    got = _latent_by_kernels(dtype, m, 1e-5, proj, W, [45] + [1] * 30, 4)
+    assert np.abs(got - want).max() <= (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("H,D,R,V,Cr,page", [(16, 32, 32, 16, 96, 16), (12, 16, 16, 24, 48, 32), (3, 64, 8, 64, 56, 16), (40, 8, 64, 8, 64, 64),
+                                             (16, 16, 0, 8, 128, 8)])
+def test_latent_attention_on_tensor_cores(H, D, R, V, Cr, page):
+    """Cached rows of 64 and 128 in bfloat16: prompt portions of 150, 9 and 60 tokens on the tcgen05 kernel with all heads on
+    the one cached row, portions of 3 and single tokens on the split-key kernel with the heads in groups of at most 8; pages
+    of 8 leave everything to the latter."""
+    rng = np.random.default_rng(H * D + Cr)
+    m = _latent_sizes(H, D, R, V, Cr)
+    W = _latent_weights(rng, m, "bfloat16")
+    T = 150 + 9 + 3 + 60 + 20
+    proj = rng.standard_normal((T, H * (D + R) + Cr + R + H)) * 1.5
+    want = C.latent_rows_plain(m, 1e-5, proj, W)
+    got = _latent_by_kernels("bfloat16", m, 1e-5, proj, W, [150, 9, 3, 60] + [1] * 20, page, tensor_cores=True)
+    assert np.abs(got - want).max() <= 3e-2 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("through", ["latent", "rotated"])
+@pytest.mark.parametrize("dtype,Cr,R,tensor_cores", [("float32", 16, 8, False), ("bfloat16", 16, 8, False), ("bfloat16", 48, 16, True),
+                                                    ("bfloat16", 96, 32, True)])
+@pytest.mark.parametrize("far,page", [(0, 16), (15, 16), (16, 16), (3, 4), (31, 8), (127, 32), (128, 64)])
+def test_a_far_position_among_hundreds(dtype, Cr, R, tensor_cores, far, page, through):
+    """One position, before, at or after a page border, outweighs the hundreds of others for the queries that look for it,
+    through the latent or through the rotated key part alone (where only the right turn by the distance finds it), in a
+    prompt of 600 and in 20 single tokens (tests/zepesun_cases.py: far_latent_case)."""
+    H = 12 if tensor_cores else 2
+    m, W, proj, seekers, v_far, want = C.far_latent_case(far, seed=far * 31 + page, T=620, prompt=600, C=Cr, R=R, H=H, through=through)
+    if dtype == "bfloat16":
+        W = dict(W, uv=_bf16_round(W["uv"]))
+        want = C.latent_rows_plain(m, 1e-5, proj, W)
+    got = _latent_by_kernels(dtype, m, 1e-5, proj, W, [600] + [1] * 20, page, tensor_cores=tensor_cores)
+    tol = (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+    assert np.abs(got - want).max() <= tol
+    for t in seekers:
+        assert np.abs(got[t, :8] - v_far[0]).max() < 0.05 * np.abs(v_far[0]).max()
+
+
+def _window_by_kernels(dtype, m, rows, bias, cuts, page, tensor_cores=False):
+    """Head preparation with biases, the windowed attention and the output gate on one request cut as `cuts`; rows: the
+    32-bit product [T, q | k | v | gate] before biases."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    nh, nkv, hd, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    width = nh * hd + nkv * (hd + vd)
+    T = len(rows)
+    n_blocks = -(-T // page)
+    n_pages = n_blocks + 3
+    table = torch.arange(n_pages - 1, n_pages - 1 - n_blocks, -1, dtype=torch.int32, device="cuda").reshape(1, -1)
+    kc = torch.zeros(n_pages * page * nkv * hd, dtype=tdt, device="cuda")
+    vc = torch.zeros(n_pages * page * nkv * vd, dtype=tdt, device="cuda")
+    status = ops.new_status("cuda")
+    window = m["mask"]["size"] if m.get("mask") else None
+    out_all, at = np.zeros((T, nh * vd)), 0
+    for n in cuts:
+        pos, iot = _dev(np.arange(at, at + n, dtype=np.int32)), _dev(np.zeros(n, dtype=np.int32))
+        starts = _dev(np.array([0, n], dtype=np.int32))
+        x = _f32(rows[at:at + n])
+        q = torch.empty(n, nh * hd, dtype=tdt, device="cuda")
+        ops.qkv_prepare_store(x[:, :width], _f32(bias), pos, iot, None, 0, None, None, None, None, q, kc, vc, table, page, n_pages,
+                              nh, nkv, hd, vd, status)
+        out = torch.empty(n, nh * vd, dtype=tdt, device="cuda")
+        done = False
+        if tensor_cores and n >= 8:
+            done = ops.attention_prefill(q, kc, vc, starts, _dev(np.array([at], dtype=np.int32)), 1, table, page, n_pages, window,
+                                         m["scale"], out, nh, nkv, hd, status)
+            assert done, "the tensor-core prompt kernel declined a shape it is said to take"
+        if not done:
+            ops.attention_any(q, kc, vc, pos, iot, table, page, n_pages, window, m["scale"], False, out, nh, nkv, hd, vd, status)
+        ops.sigmoid_gate(out, x[:, width:])
+        out_all[at:at + n] = out.float().cpu().numpy()
+        at += n
+    ops.read_status(status)
+    return out_all
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,vd,window", [(4, 2, 16, 16, 9), (6, 1, 8, 12, None), (3, 3, 24, 8, 70), (6, 2, 48, 48, 40), (2, 2, 12, 12, 1)])
+def test_gated_window_attention_kernels(dtype, nh, nkv, hd, vd, window):
+    """Biases, no rotation, the window, grouped heads, a value size of its own and the gate per output element: a prompt of
+    45 tokens, then 30 tokens one by one on the same cache (pages of 4: every border is crossed)."""
+    rng = np.random.default_rng(hd + vd)
+    m = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": vd, "scale": 0.35}
+    if window:
+        m["mask"] = {"size": window}
+    width = nh * hd + nkv * (hd + vd)
+    rows, bias = rng.standard_normal((75, width + nh * vd)), rng.standard_normal(width) * 0.5
+    want = C.window_rows_plain(m, rows, bias)
+    got = _window_by_kernels(dtype, m, rows, bias, [45] + [1] * 30, 4)
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 2.5e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype,hd,tensor_cores", [("float32", 32, False), ("bfloat16", 32, False), ("bfloat16", 64, True)])
+@pytest.mark.parametrize("size,page", [(16, 16), (17, 16), (33, 8), (5, 4), (64, 16), (40, 32)])
+def test_a_key_just_inside_and_just_outside_the_window(dtype, hd, tensor_cores, size, page):
+    """Marked keys before, at and after page borders score far above all others for queries that point their way.  The
+    query `size - 1` positions after one still sees it and returns its marked value; the next query does not
+    (tests/zepesun_cases.py: window_edge_case).  The queries come in a prompt of 230 and decoded one by one; with
+    tensor_cores the prompt goes through the tcgen05 kernel where it takes the page size."""
+    m, rows, bias, alone, want = C.window_edge_case(size, hd, seed=size * 7 + page + hd, T=260)
+    got = _window_by_kernels(dtype, m, rows, bias, [230] + [1] * 30, page, tensor_cores=tensor_cores and page in (16, 32, 64, 128))
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+    assert alone
+    for p in alone:
+        assert np.abs(got[p + size - 1, :hd] - 5.0).max() < 0.2
+        assert np.abs(got[p + size, :hd] - 5.0).max() > 1.5
+
+
+@pytest.mark.parametrize("E,top,groups,keep,scale", [(16, 4, 4, 3, 2.0), (6, 2, 3, 2, 1.7), (8, 2, 2, 1, 1.0), (5, 5, 1, 1, 2.0), (3, 2, 3, 3, 3.0),
+                                                     (64, 6, 8, 2, 1.0), (40, 3, 40, 5, 0.5)])
+def test_router_with_groups(E, top, groups, keep, scale):
+    """Softmax scores over all experts, only the best groups' experts as candidates, the chosen scores renormalised and
+    scaled, from the 32-bit kernel and from logits a product made; with and without an expert that every row uses."""
+    import torch
+    from imparo_b200.kernels import ops
+    rng = np.random.default_rng(E * top)
+    width, T = 48, 37
+    h, wr = _bf16_round(rng.standard_normal((T, width))), rng.standard_normal((E, width)) * 0.5
+    ids_w, wts_w = P.route(h @ wr.T, top, groups, keep, scale)
+    for always in (0, 1):
+        ids = torch.zeros(T, top + always, dtype=torch.int32, device="cuda")
+        wts = torch.zeros(T, top + always, dtype=torch.float32, device="cuda")
+        how = dict(softmax=True, renormalise=True, groups=groups, keep=keep, renorm_eps=1e-20, weight_scale=scale, always=always)
+        ops.moe_route(_f32(h), _f32(wr), top, ids, wts, **how)
+        assert np.array_equal(ids.cpu().numpy()[:, :top], ids_w)
+        assert np.abs(wts.cpu().numpy()[:, :top] - wts_w).max() <= 1e-5 * scale
+        logits = _f32(h @ wr.T)
+        ids.zero_(); wts.zero_()
+        ops.moe_pick(logits, E, 1, top, ids, wts, **how)
+        assert np.array_equal(ids.cpu().numpy()[:, :top], ids_w)
+        if always:
+            assert (ids.cpu().numpy()[:, top] == E).all() and (wts.cpu().numpy()[:, top] == 1.0).all()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,top,ff,width,limit,shared_ff", [(5, 6, 2, 24, 64, 1.5, 24), (40, 8, 3, 32, 128, 1.0, 64), (300, 8, 2, 64, 128, 1.0, 64),
+                                                               (70, 4, 1, 16, 52, 0.8, None), (150, 16, 4, 96, 320, 1.0, 96)])
+def test_clamped_experts_with_a_shared_one(dtype, T, E, top, ff, width, limit, shared_ff):
+    """The routed feed-forward as a part: clamped experts pair by pair, sorted into small tiles and on the tensor-memory
+    product, with a shared expert of the experts' size (stacked behind them), of another size (a pass of its own) or none."""
+    import torch
+    from imparo_b200.kernels import ops
+    from imparo_b200.parts.base import Runtime, Workspace
+    from imparo_b200.parts.moe import RoutedExperts
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(T + E)
+    rnd = (lambda a: a) if dtype == "float32" else _bf16_round
+    mlp = {"router": {"experts": E, "top": top, "scale": 2.0, "groups": {"count": 2 if E % 2 == 0 else 1, "keep": 1 if E >= 8 else 2 if E % 2 == 0 else 1}},
+           "expert": {"ff": ff, "limit": limit}}
+    if top > E // 2:
+        mlp["router"]["groups"] = {"count": 1, "keep": 1}
+    W = {"router": rnd(rng.standard_normal((E, width)) * 0.5)}
+    for e in range(E):
+        W.update({f"e{e}.gate": rnd(rng.standard_normal((ff, width)) / np.sqrt(width) * 1.5), f"e{e}.up": rnd(rng.standard_normal((ff, width)) / np.sqrt(width) * 1.5),
+                  f"e{e}.down": rnd(rng.standard_normal((width, ff)) / np.sqrt(ff))})
+    shared = None
+    if shared_ff:
+        mlp["shared"] = {"ff": shared_ff, "limit": limit if shared_ff == ff else 2.5}
+        shared = dict(mlp["shared"])
+        W.update({"shared.gate": rnd(rng.standard_normal((shared_ff, width)) / np.sqrt(width)), "shared.up": rnd(rng.standard_normal((shared_ff, width)) / np.sqrt(width)),
+                  "shared.down": rnd(rng.standard_normal((width, shared_ff)) / np.sqrt(shared_ff))})
+    h = rnd(rng.standard_normal((T, width)))
+    want = P.moe_ff(h, W, "", mlp)
+    status = ops.new_status("cuda")
+    rt = Runtime(precision=dtype, device=torch.device("cuda"), status=status, workspace=Workspace(torch.device("cuda")))
+    g = mlp["router"]["groups"]
+    part = RoutedExperts({"hidden": width, "ff": ff, "experts": E, "top": top, "score": "softmax", "renormalise": True, "renorm_eps": 1e-20,
+                          "weight_scale": 2.0, "groups": g["count"], "keep": g["keep"], "act": "clamped_swish", "limit": limit, "shared": shared}, "", rt)
+    part.bind({w.name: _dev(W[w.name], torch.float32 if w.role == "vector" else tdt) for w in part.weight_specs()})
+    assert part.shared_stacked == (shared_ff == ff)
+    out = torch.zeros(T, width, device="cuda")
+    part.forward(_dev(h, tdt), None, out)
+    ops.read_status(status)
+    assert np.abs(out.cpu().numpy() - want).max() <= (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+    base = torch.ones(T, width, device="cuda")
+    part.forward(_dev(h, tdt), None, base, accumulate=True)
+    assert np.abs(base.cpu().numpy() - 1.0 - want).max() <= (3e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_kernels(dtype):
+    """The gated activations with biases, the embedding with position vectors, the weighted sum of branches, the per-head
+    norm with each head's own weight, the gate per group of columns."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rnd = (lambda a: a) if dtype == "float32" else _bf16_round
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    rng = np.random.default_rng(5)
+    T, F = 19, 37
+    gu, bias = rnd(rng.standard_normal((T, 2 * F)) * 2.0), rng.standard_normal(2 * F)
+    out = torch.empty(T, F, dtype=tdt, device="cuda")
+    ops.gated_act(_dev(gu, tdt), out, "gelu_tanh", bias=_f32(bias))
+    want = P.gelu_tanh(gu[:, :F] + bias[:F]) * (gu[:, F:] + bias[F:])
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+    ops.gated_act(_dev(gu, tdt), out, "clamped_swish", limit=0.7)
+    g, u = np.minimum(gu[:, :F], 0.7), np.clip(gu[:, F:], -0.7, 0.7)
+    want = g * P.sigmoid(1.702 * g) * (u + 1.0)
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+    # embedding: the row times a factor plus the position's row, unscaled
+    width = 40
+    table, pos_t = rnd(rng.standard_normal((50, width))), rnd(rng.standard_normal((30, width)))
+    ids, pos = rng.integers(0, 50, T).astype(np.int32), rng.integers(0, 30, T).astype(np.int32)
+    e = torch.empty(T, width, device="cuda")
+    status = ops.new_status("cuda")
+    ops.embed_copies(_dev(table, tdt), _dev(ids), e, status, scale=3.0, pos_table=_dev(pos_t, tdt), positions=_dev(pos))
+    ops.read_status(status)
+    assert np.abs(e.cpu().numpy() - (table[ids] * 3.0 + pos_t[pos])).max() <= 1e-6 * 10
+    pos[3] = 30                                                     # beyond the table: reported, not read
+    ops.embed_copies(_dev(table, tdt), _dev(ids), e, status, scale=3.0, pos_table=_dev(pos_t, tdt), positions=_dev(pos))
+    with pytest.raises(Exception):
+        ops.read_status(status)
+    # the weighted sum of branches
+    x, ys = rng.standard_normal((T, width)), [rng.standard_normal((T, width)) for _ in range(3)]
+    xd = _f32(x)
+    ops.add_weighted(xd, [_f32(y) for y in ys], [1.2, 0.5, -2.0])
+    assert np.abs(xd.cpu().numpy() - (x + 1.2 * ys[0] + 0.5 * ys[1] - 2.0 * ys[2])).max() <= 1e-5
+    # per-head norm, each head its own weight, a gate per element
+    H, V = 3, 20
+    o, w, gate = rng.standard_normal((T, H * V)) * 4.0, rng.uniform(0.5, 1.5, H * V), rng.standard_normal((T, H * V))
+    y = torch.empty(T, H * V, dtype=tdt, device="cuda")
+    ops.head_norm_gate(_f32(o), _f32(w), 1e-5, _f32(gate), y, H, V)
+    want = (P.unit_rms(o.reshape(T, H, V), 1e-5).reshape(T, H * V) * w) * P.sigmoid(gate)
+    assert np.abs(y.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+    # a gate per head
+    xg = rnd(rng.standard_normal((T, H * V)))
+    xd = _dev(xg, tdt)
+    ops.sigmoid_gate(xd, _f32(gate[:, :H]), group=V)
+    want = xg * np.repeat(P.sigmoid(gate[:, :H]), V, axis=1)
+    assert np.abs(xd.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+
+
+# ---- generation ------------------------------------------------------------------------------------------------
+
+def plain_generate(name, prompt, n_new):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(n_new):
+        row = plain_logits(name, {"g": toks})["g"][-1]
+        t = int(np.argmax(row))
+        top2 = np.partition(row, -2)[-2:]
+        out.append(t)
+        margins.append(float(top2[1] - top2[0]))
+        toks.append(t)
+    return out, margins
+
+
+@pytest.mark.parametrize("dtype,min_margin", [("float32", 1e-3), ("bfloat16", 1.0)])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_scheduler(name, dtype, min_margin):
+    """Three prompts through Engine.generate: continuous batching with prompt portions of at most 8 tokens beside
+    decoding requests, two state slots for three requests, pages used again."""
+    from imparo_b200.engine import Engine
+    from tests.test_generate_gpu import agree
+    prompts = list(make_requests(name, [5, 23, 40], seed=1).values())
+    page = PAGE[name]
+    eng = Engine(model_dir(name), dtype=dtype, ctx=64, parallel=2, page_size=page, num_pages=2 * (64 // page), max_step_tokens=8)
+    got = eng.generate(prompts, max_tokens=10)
+    for i, p in enumerate(prompts):
+        want, margins = plain_generate(name, p, 10)
+        agree(got[i], want, margins, min_margin)
+    assert eng.cache.n_requests() == 0
+    eng.cache.check()
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    from tests.test_trace_run_gpu import replay
+    name = "A"
+    prompt = make_requests(name, [16], seed=0)["r0"]
+    want, _ = plain_generate(name, prompt, 6)
+    tf = tmp_path / "tokens.txt"
+    tf.write_text(" ".join(map(str, prompt)))
+    r = subprocess.run([sys.executable, "-m", "imparo_b200", "-m", model_dir(name), "--dtype", "float32", "--decode", "6",
+                        "-c", "64", "-t", str(tf), "--json"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["tokens"] == [want]
+    reqs = make_requests(name, [70, 33, 90, 41, 64, 52], seed=7)
+    steps = traces.mixed(reqs, seed=1)
+    max_tokens = traces.max_live_tokens(steps, 64)
+    out = tmp_path / "out"
+    replay(model_dir(name), "bfloat16", steps, out, max_tokens)
+    ref = plain_logits(name, reqs)
+    want = traces.expected(steps, ref)
+    got = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, ALL[name]["vocab"]) for s in steps if s["step"] in want}
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    skip = close_calls(name, reqs)
+    errs = [e for e in all_errors(steps, got, want) if (e[1], e[2]) not in skip]
+    assert max(e[3] for e in errs) <= WORST["bfloat16"] * scale
+    assert sum(e[3] > TOL["bfloat16"] * scale for e in errs) <= 0.1 * len(errs)
