@@ -65,16 +65,19 @@ latent_rot_store_kernel(const float* __restrict__ proj, size_t stride, int heads
                         T* __restrict__ q_plain, T* __restrict__ q_lat, T* __restrict__ cache, const int* __restrict__ table,
                         int max_blocks, int page_size, int n_pages, int* status) {
     __shared__ float scratch[33];
+    __shared__ float cs_s[256], sn_s[256];         // the position's cosines and sines, once for all heads (n_rot <= 512)
     pdl_trigger();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int blk = pos / page_size;
     int page = -1;
     if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
-    pdl_wait();
-    const float* row = proj + (size_t)t * stride;
     const int q_width = heads * (dim + rot), row_w = rank + rot, half = n_rot / 2;
     const float fpos = (float)pos;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(fpos * inv_freq[j], &sn_s[j], &cs_s[j]);
+    pdl_wait();
+    __syncthreads();
+    const float* row = proj + (size_t)t * stride;
     // queries: plain dimensions as they are, rotated ones turned
     for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
         const int h = i / dim, d = i % dim;
@@ -86,8 +89,7 @@ latent_rot_store_kernel(const float* __restrict__ proj, size_t stride, int heads
         float v = qr[d];
         if (d < n_rot) {
             const int j = d < half ? d : d - half;
-            float sn, cs;
-            sincosf(fpos * inv_freq[j], &sn, &cs);
+            const float sn = sn_s[j], cs = cs_s[j];
             v = d < half ? qr[d] * cs - qr[d + half] * sn : qr[d] * cs + qr[d - half] * sn;
         }
         q_lat[((size_t)t * heads + h) * row_w + rank + d] = from_f32<T>(v);
@@ -109,8 +111,7 @@ latent_rot_store_kernel(const float* __restrict__ proj, size_t stride, int heads
         float v = kr[d];
         if (d < n_rot) {
             const int j = d < half ? d : d - half;
-            float sn, cs;
-            sincosf(fpos * inv_freq[j], &sn, &cs);
+            const float sn = sn_s[j], cs = cs_s[j];
             v = d < half ? kr[d] * cs - kr[d + half] * sn : kr[d] * cs + kr[d - half] * sn;
         }
         dst[rank + d] = from_f32<T>(v);
@@ -218,7 +219,7 @@ extern "C" int imparo_latent_rot_store(const float* proj, long long stride, int 
                                        void* q_plain, void* q_lat, void* cache, int dtype, const int* table, int max_blocks,
                                        int page_size, int n_pages, int n_tok, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
-    if (heads < 1 || dim < 1 || rot < 0 || rank < 1 || n_rot < 0 || n_rot > rot || n_rot % 2 || (n_rot > 0 && inv_freq == nullptr)
+    if (heads < 1 || dim < 1 || rot < 0 || rank < 1 || n_rot < 0 || n_rot > rot || n_rot > 512 || n_rot % 2 || (n_rot > 0 && inv_freq == nullptr)
         || stride < (long long)heads * (dim + rot) + rank + rot) return -2;
     if (dtype == IMPARO_DT_F32)
         launch(latent_rot_store_kernel<float>, dim3(n_tok), dim3(128), 0, stream, proj, (size_t)stride, heads, dim, rot, rank, wc, eps,

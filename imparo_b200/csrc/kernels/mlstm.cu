@@ -12,10 +12,12 @@
 // token by token, runs the same sequence of operations as the whole prompt.  q, k, v and the gates' pre-activations are
 // columns of one 32-bit product; everything here is 32-bit.
 //
-//  (1) mlstm_recurrent: one warp per (request, head, 32 value columns).  A lane owns one column of S in registers (dim
-//      values); n is spread over the lanes (entry d with lane d % 32) and m is kept by every lane; the rows are staged 16
-//      at a time in shared memory.  Every warp of a head repeats n and m and keeps a copy of its own in the slot (n is
-//      [heads, vblocks, dim], m [heads, vblocks], vblocks = ceil(vdim / 32)): no warp reads what another one writes.
+//  (1) mlstm_recurrent: one warp per (request, head, 32 value columns), up to four warps of one head in a CTA.  A lane owns
+//      one column of S in registers (dim values); n is spread over the lanes (entry d with lane d % 32) and m is kept by
+//      every lane; the rows' k, q, v and gate inputs are copied asynchronously into shared memory a stage of 8 or 16 rows
+//      ahead, k and q once for the CTA's warps.  Every warp of a head repeats n and m and keeps a copy of its own in the
+//      slot (n is [heads, vblocks, dim], m [heads, vblocks], vblocks = ceil(vdim / 32)): no warp reads what another one
+//      writes.
 //  (2) long portions in chunks of `chunk` rows that run side by side, in three launches.  With b_t the sum of the log
 //      forget gates from the chunk's first row to row t, the recurrence unrolls to
 //          m_t = max(b_t + m_in, max_(s<=t) (b_t - b_s + a_s))
@@ -30,8 +32,6 @@
 
 namespace imparo {
 
-constexpr int ML_STAGE = 16;
-
 __device__ __forceinline__ float ml_log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 struct MlstmCols {
@@ -43,87 +43,139 @@ struct MlstmCols {
     float cap, q_scale;
 };
 
-// Rows [r_begin, r_end) of one request and head, for the 32 value columns of this warp.  S: this lane's column of the
-// state; nl: this lane's entries of n (d = lane, lane + 32, ...); m: the running maximum (-INFINITY: an empty state).
-// out: null when only the state is wanted.
-template <int DMAX>
-__device__ __forceinline__ void ml_walk(const MlstmCols& c, float (&S)[DMAX], float (&nl)[DMAX / 32], float& m, int r_begin, int r_end,
-                                        float* __restrict__ out, int h, int heads, int dim, int vdim, int col, bool live,
-                                        float (*qs)[DMAX], float (*ks)[DMAX], float (*vs)[32], float (*gs)[2], float* total_f) {
-    const int lane = threadIdx.x;
-    float fsum = 0.f;
-    for (int base = r_begin; base < r_end; base += ML_STAGE) {
-        const int n = min(ML_STAGE, r_end - base);
-        __syncwarp();
-        for (int r = 0; r < n; ++r) {
+// A CTA is NW warps: warp w owns value columns [(blockIdx.z * NW + w) * 32, +32) of one (request or chunk, head).  The rows'
+// k, q, v and gate inputs pass through shared memory in stages of ST rows that all threads copy asynchronously (cp.async, 4
+// bytes each) one stage ahead of the one being walked; k and q are shared by the CTA's warps.
+template <int DMAX> struct MlStage { static constexpr int ROWS = DMAX <= 64 ? 16 : 8; };
+
+template <int DMAX, int NW>
+struct MlSmem {
+    static constexpr int ST = MlStage<DMAX>::ROWS;
+    float k[2][ST][DMAX];
+    float q[2][ST][DMAX];
+    float v[2][ST][NW * 32];
+    float x[2][ST][2];          // the gates' inputs as the product left them
+    float g[ST][2];             // log input gate, log forget gate
+};
+
+__device__ __forceinline__ void ml_cp_async4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ml_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void ml_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Rows [r_begin, r_end) of one request and head.  S: this lane's column of the state; nl: this lane's entries of n
+// (d = lane, lane + 32, ...); m: the running maximum (-INFINITY: an empty state).  OUT: the rows' outputs are wanted (else
+// only the state, and q is not read).  Every thread of the CTA calls this with the same rows; `live`: this lane has a column.
+template <int DMAX, int NW, bool OUT>
+__device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm, float (&S)[DMAX], float (&nl)[DMAX / 32], float& m,
+                                        int r_begin, int r_end, float* __restrict__ out, int h, int heads, int dim, int vdim,
+                                        int v0, int col, bool live, float* total_f) {
+    constexpr int ST = MlSmem<DMAX, NW>::ST;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = NW * 32;
+    const int vcols = min(NW * 32, vdim - v0);
+    // columns no copy writes: zero once
+    for (int i = tid; i < 2 * ST * DMAX; i += nthreads) {
+        const int d = i % DMAX;
+        if (d >= dim || !OUT) (&sm.q[0][0][0])[i] = 0.f;
+        if (d >= dim) (&sm.k[0][0][0])[i] = 0.f;
+    }
+    for (int i = tid; i < 2 * ST * NW * 32; i += nthreads)
+        if (i % (NW * 32) >= vcols) (&sm.v[0][0][0])[i] = 0.f;
+    const int per_row = dim + (OUT ? dim : 0) + vcols + 2;
+    auto issue = [&](int base, int n, int buf) {
+        for (int e = tid; e < n * per_row; e += nthreads) {
+            const int r = e / per_row;
+            int cidx = e - r * per_row;
             const float* row = c.proj + (size_t)(base + r) * c.stride;
-            const float* qr = row + c.q_off + (size_t)h * dim;
-            const float* kr = row + c.k_off + (size_t)h * dim;
-            for (int d = lane; d < DMAX; d += 32) {
-                qs[r][d] = (d < dim && out) ? qr[d] * c.q_scale : 0.f;
-                ks[r][d] = d < dim ? kr[d] : 0.f;
+            if (cidx < dim) { ml_cp_async4(&sm.k[buf][r][cidx], row + c.k_off + (size_t)h * dim + cidx); continue; }
+            cidx -= dim;
+            if (OUT) {
+                if (cidx < dim) { ml_cp_async4(&sm.q[buf][r][cidx], row + c.q_off + (size_t)h * dim + cidx); continue; }
+                cidx -= dim;
             }
-            vs[r][lane] = live ? row[c.v_off + (size_t)h * vdim + col] : 0.f;
+            if (cidx < vcols) { ml_cp_async4(&sm.v[buf][r][cidx], row + c.v_off + (size_t)h * vdim + v0 + cidx); continue; }
+            cidx -= vcols;
+            ml_cp_async4(&sm.x[buf][r][cidx], row + (cidx == 0 ? c.i_off : c.f_off) + h);
         }
-        if (lane < n) {
-            const float* row = c.proj + (size_t)(base + lane) * c.stride;
-            const float xi = row[c.i_off + h] + c.i_bias[h], xf = row[c.f_off + h] + c.f_bias[h];
-            gs[lane][0] = c.cap * tanhf(xi / c.cap);
-            gs[lane][1] = ml_log_sigmoid(c.cap * tanhf(xf / c.cap));
+        ml_cp_commit();
+    };
+    float fsum = 0.f;
+    const int total = r_end - r_begin;
+    const int n_stages = (total + ST - 1) / ST;
+    if (n_stages > 0) issue(r_begin, min(ST, total), 0);
+    const float bi = c.i_bias[h], bf = c.f_bias[h];
+    for (int s = 0; s < n_stages; ++s) {
+        const int base = r_begin + s * ST, n = min(ST, r_end - base), buf = s & 1;
+        if (s + 1 < n_stages) {
+            issue(base + ST, min(ST, r_end - base - ST), buf ^ 1);
+            ml_cp_wait<1>();
+        } else {
+            ml_cp_wait<0>();
         }
-        __syncwarp();
+        __syncthreads();
+        if (tid < n) {
+            sm.g[tid][0] = c.cap * tanhf((sm.x[buf][tid][0] + bi) / c.cap);
+            sm.g[tid][1] = ml_log_sigmoid(c.cap * tanhf((sm.x[buf][tid][1] + bf) / c.cap));
+        }
+        __syncthreads();
         for (int r = 0; r < n; ++r) {
-            const float a = gs[r][0], f = gs[r][1];
+            const float a = sm.g[r][0], f = sm.g[r][1];
             fsum += f;
             const float m_new = fmaxf(f + m, a);
             const float keep = expf(f + m - m_new);       // an empty state (m = -inf) keeps nothing: exp(-inf) = 0
             const float put = expf(a - m_new);
             m = m_new;
-            const float pv = put * vs[r][lane];
-            float o = 0.f, nq = 0.f;
+            const float pv = put * sm.v[buf][r][warp * 32 + lane];
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, nq = 0.f;
 #pragma unroll
             for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[r][d]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[r][d]);
-                S[d] = keep * S[d] + k4.x * pv;         o += S[d] * q4.x;
-                S[d + 1] = keep * S[d + 1] + k4.y * pv; o += S[d + 1] * q4.y;
-                S[d + 2] = keep * S[d + 2] + k4.z * pv; o += S[d + 2] * q4.z;
-                S[d + 3] = keep * S[d + 3] + k4.w * pv; o += S[d + 3] * q4.w;
+                const float4 k4 = *reinterpret_cast<const float4*>(&sm.k[buf][r][d]);
+                S[d] = keep * S[d] + k4.x * pv;
+                S[d + 1] = keep * S[d + 1] + k4.y * pv;
+                S[d + 2] = keep * S[d + 2] + k4.z * pv;
+                S[d + 3] = keep * S[d + 3] + k4.w * pv;
+                if (OUT) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(&sm.q[buf][r][d]);
+                    o0 += S[d] * q4.x; o1 += S[d + 1] * q4.y; o2 += S[d + 2] * q4.z; o3 += S[d + 3] * q4.w;
+                }
             }
 #pragma unroll
             for (int j = 0; j < DMAX / 32; ++j) {
-                nl[j] = keep * nl[j] + put * ks[r][j * 32 + lane];
-                nq += nl[j] * qs[r][j * 32 + lane];
+                nl[j] = keep * nl[j] + put * sm.k[buf][r][j * 32 + lane];
+                if (OUT) nq += nl[j] * sm.q[buf][r][j * 32 + lane];
             }
-            if (out) {
-                nq = warp_sum(nq);
+            if (OUT) {
+                nq = warp_sum(nq) * c.q_scale;
                 const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
-                if (live) out[(size_t)(base + r) * ((size_t)heads * vdim) + (size_t)h * vdim + col] = o / den;
+                if (live) out[(size_t)(base + r) * ((size_t)heads * vdim) + (size_t)h * vdim + col] = ((o0 + o1) + (o2 + o3)) * c.q_scale / den;
             }
         }
+        __syncthreads();          // the stage after the next one is copied into this buffer
     }
     if (total_f) *total_f = fsum;
 }
 
-template <int DMAX>
-__global__ void __launch_bounds__(32)
+template <int DMAX, int NW>
+__global__ void __launch_bounds__(NW * 32)
 mlstm_recurrent_kernel(MlstmCols c, float* __restrict__ state_S, float* __restrict__ state_n, float* __restrict__ state_m,
                        const int* __restrict__ item_row_start, const int* __restrict__ item_slot, int n_slots,
-                       float* __restrict__ out, int heads, int dim, int vdim, int* status) {
-    __shared__ __align__(16) float qs[ML_STAGE][DMAX], ks[ML_STAGE][DMAX], vs[ML_STAGE][32], gs[ML_STAGE][2];
+                       float* __restrict__ out, int heads, int dim, int vdim, int vblocks, int* status) {
+    __shared__ __align__(16) MlSmem<DMAX, NW> sm;
     pdl_trigger();
-    const int item = blockIdx.x, h = blockIdx.y, col = blockIdx.z * 32 + threadIdx.x;
-    const int lane = threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int item = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * 32, vb = blockIdx.z * NW + warp, col = v0 + warp * 32 + lane;
     const int r0 = item_row_start[item], r1 = item_row_start[item + 1];
     const int slot = item_slot[item];
     pdl_wait();
     if (slot < 0 || slot >= n_slots) {
-        if (lane == 0) report(status, IMPARO_ST_SLOT_RANGE, 81, item, slot);
+        if (threadIdx.x == 0) report(status, IMPARO_ST_SLOT_RANGE, 81, item, slot);
         return;
     }
-    const bool live = col < vdim;
+    const bool live = col < vdim, mine = vb < vblocks;
     float* sp = state_S + (((size_t)slot * heads + h) * dim) * vdim + col;
-    const size_t copy = ((size_t)slot * heads + h) * gridDim.z + blockIdx.z;
+    const size_t copy = ((size_t)slot * heads + h) * vblocks + (mine ? vb : 0);
     float* np = state_n + copy * dim;
     float* mp = state_m + copy;
     float S[DMAX], nl[DMAX / 32];
@@ -132,14 +184,16 @@ mlstm_recurrent_kernel(MlstmCols c, float* __restrict__ state_S, float* __restri
 #pragma unroll
     for (int j = 0; j < DMAX / 32; ++j) nl[j] = (j * 32 + lane < dim) ? np[j * 32 + lane] : 0.f;
     float m = *mp;
-    ml_walk<DMAX>(c, S, nl, m, r0, r1, out, h, heads, dim, vdim, col, live, qs, ks, vs, gs, nullptr);
+    ml_walk<DMAX, NW, true>(c, sm, S, nl, m, r0, r1, out, h, heads, dim, vdim, v0, col, live, nullptr);
     if (live) {
 #pragma unroll
         for (int d = 0; d < DMAX; ++d) if (d < dim) sp[(size_t)d * vdim] = S[d];
     }
+    if (mine) {
 #pragma unroll
-    for (int j = 0; j < DMAX / 32; ++j) if (j * 32 + lane < dim) np[j * 32 + lane] = nl[j];
-    if (lane == 0) *mp = m;
+        for (int j = 0; j < DMAX / 32; ++j) if (j * 32 + lane < dim) np[j * 32 + lane] = nl[j];
+        if (lane == 0) *mp = m;
+    }
 }
 
 // ---- long portions in chunks ---------------------------------------------------------------------------------------
@@ -166,22 +220,22 @@ __device__ __forceinline__ bool ml_find_chunk(const int* __restrict__ item_row_s
 // chunk_S [chunks, heads, dim, vdim], chunk_n [chunks, heads, vblocks, dim], chunk_mb [chunks, heads, vblocks, 3] = (the
 // chunk's own maximum, its total b, the maximum it starts from).  The out pass of a request's last chunk leaves the slot's
 // maximum.
-template <int DMAX, bool OUT>
-__global__ void __launch_bounds__(32)
+template <int DMAX, int NW, bool OUT>
+__global__ void __launch_bounds__(NW * 32)
 mlstm_chunk_kernel(MlstmCols c, float* __restrict__ chunk_S, float* __restrict__ chunk_n, float* __restrict__ chunk_mb,
                    const int* __restrict__ item_row_start, int n_items, int chunk, float* __restrict__ out, int heads, int dim,
-                   int vdim, const int* __restrict__ item_slot, int n_slots, float* __restrict__ state_m) {
-    __shared__ __align__(16) float qs[ML_STAGE][DMAX], ks[ML_STAGE][DMAX], vs[ML_STAGE][32], gs[ML_STAGE][2];
+                   int vdim, int vblocks, const int* __restrict__ item_slot, int n_slots, float* __restrict__ state_m) {
+    __shared__ __align__(16) MlSmem<DMAX, NW> sm;
     pdl_trigger();
-    const int g = blockIdx.x, h = blockIdx.y, col = blockIdx.z * 32 + threadIdx.x;
-    const int lane = threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * 32, vb = blockIdx.z * NW + warp, col = v0 + warp * 32 + lane;
     int item, r_begin, r_end, first;
     const bool found = ml_find_chunk(item_row_start, n_items, chunk, g, item, r_begin, r_end, first);
     pdl_wait();
     if (!found) return;
-    const bool live = col < vdim;
+    const bool live = col < vdim, mine = vb < vblocks;
     float* sp = chunk_S + (((size_t)g * heads + h) * dim) * vdim + col;
-    const size_t copy = ((size_t)g * heads + h) * gridDim.z + blockIdx.z;
+    const size_t copy = ((size_t)g * heads + h) * vblocks + (mine ? vb : 0);
     float* np = chunk_n + copy * dim;
     float* mb = chunk_mb + copy * 3;
     float S[DMAX], nl[DMAX / 32];
@@ -192,10 +246,10 @@ mlstm_chunk_kernel(MlstmCols c, float* __restrict__ chunk_S, float* __restrict__
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) nl[j] = (j * 32 + lane < dim) ? np[j * 32 + lane] : 0.f;
         m = mb[2];
-        ml_walk<DMAX>(c, S, nl, m, r_begin, r_end, out, h, heads, dim, vdim, col, live, qs, ks, vs, gs, nullptr);
-        if (lane == 0 && r_end == item_row_start[item + 1]) {
+        ml_walk<DMAX, NW, true>(c, sm, S, nl, m, r_begin, r_end, out, h, heads, dim, vdim, v0, col, live, nullptr);
+        if (mine && lane == 0 && r_end == item_row_start[item + 1]) {
             const int slot = item_slot[item];
-            if (slot >= 0 && slot < n_slots) state_m[((size_t)slot * heads + h) * gridDim.z + blockIdx.z] = m;
+            if (slot >= 0 && slot < n_slots) state_m[((size_t)slot * heads + h) * vblocks + vb] = m;
         }
         return;
     }
@@ -204,14 +258,16 @@ mlstm_chunk_kernel(MlstmCols c, float* __restrict__ chunk_S, float* __restrict__
 #pragma unroll
     for (int j = 0; j < DMAX / 32; ++j) nl[j] = 0.f;
     m = -INFINITY;
-    ml_walk<DMAX>(c, S, nl, m, r_begin, r_end, nullptr, h, heads, dim, vdim, col, live, qs, ks, vs, gs, &total);
+    ml_walk<DMAX, NW, false>(c, sm, S, nl, m, r_begin, r_end, nullptr, h, heads, dim, vdim, v0, col, live, &total);
     if (live) {
 #pragma unroll
         for (int d = 0; d < DMAX; ++d) if (d < dim) sp[(size_t)d * vdim] = S[d];
     }
+    if (mine) {
 #pragma unroll
-    for (int j = 0; j < DMAX / 32; ++j) if (j * 32 + lane < dim) np[j * 32 + lane] = nl[j];
-    if (lane == 0) { mb[0] = m; mb[1] = total; mb[2] = 0.f; }
+        for (int j = 0; j < DMAX / 32; ++j) if (j * 32 + lane < dim) np[j * 32 + lane] = nl[j];
+        if (lane == 0) { mb[0] = m; mb[1] = total; mb[2] = 0.f; }
+    }
 }
 
 // grid (requests, heads, ceil((dim * vdim + vblocks * dim) / 256)): a thread per entry of S (and of every copy of n), walking
@@ -239,16 +295,31 @@ mlstm_chunk_scan_kernel(float* __restrict__ chunk_S, float* __restrict__ chunk_n
     const size_t sh = (size_t)slot * heads + h;
     float* sv = is_n ? state_n + sh * vblocks * dim + (e - n_S) : state_S + sh * n_S + e;
     float val = *sv, m = state_m[sh * vblocks];
-    for (int cidx = 0; cidx < nc; ++cidx) {
-        const size_t g = (size_t)(first + cidx) * heads + h;
-        float* lv = is_n ? chunk_n + g * vblocks * dim + (e - n_S) : chunk_S + g * n_S + e;
-        const float m_loc = chunk_mb[g * vblocks * 3], b = chunk_mb[g * vblocks * 3 + 1];
-        const float local = *lv;
-        *lv = val;                                             // the state this chunk starts from
-        if (e < vblocks) chunk_mb[(g * vblocks + e) * 3 + 2] = m;      // and its maximum (an entry no thread reads here)
-        const float m_new = fmaxf(b + m, m_loc);
-        val = expf(b + m - m_new) * val + expf(m_loc - m_new) * local;
-        m = m_new;
+    const size_t per_chunk = is_n ? (size_t)heads * vblocks * dim : (size_t)heads * n_S;
+    float* lv0 = is_n ? chunk_n + ((size_t)first * heads + h) * vblocks * dim + (e - n_S) : chunk_S + ((size_t)first * heads + h) * n_S + e;
+    for (int c0 = 0; c0 < nc; c0 += 4) {
+        // four chunks' loads at once (they depend on nothing), then the four dependent steps
+        float local[4], m_loc[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (c0 + u < nc) {
+                const size_t g = (size_t)(first + c0 + u) * heads + h;
+                local[u] = lv0[(size_t)(c0 + u) * per_chunk];
+                m_loc[u] = chunk_mb[g * vblocks * 3];
+                b[u] = chunk_mb[g * vblocks * 3 + 1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (c0 + u < nc) {
+                const size_t g = (size_t)(first + c0 + u) * heads + h;
+                lv0[(size_t)(c0 + u) * per_chunk] = val;                          // the state this chunk starts from
+                if (e < vblocks) chunk_mb[(g * vblocks + e) * 3 + 2] = m;         // and its maximum (an entry no thread reads here)
+                const float m_new = fmaxf(b[u] + m, m_loc[u]);
+                val = expf(b[u] + m - m_new) * val + expf(m_loc[u] - m_new) * local[u];
+                m = m_new;
+            }
+        }
     }
     *sv = val;
 }
@@ -257,29 +328,46 @@ mlstm_chunk_scan_kernel(float* __restrict__ chunk_S, float* __restrict__ chunk_n
 
 using namespace imparo;
 
-template <int DMAX>
-static int mlstm_launch(const MlstmCols& c, float* S, float* n, float* m, const int* item_row_start, const int* item_slot, int n_slots,
-                        int n_items, int n_tok, float* out, int heads, int dim, int vdim, int chunk, float* chunk_S, float* chunk_n,
-                        float* chunk_mb, int* status, cudaStream_t stream) {
+template <int DMAX, int NW>
+static int mlstm_launch_nw(const MlstmCols& c, float* S, float* n, float* m, const int* item_row_start, const int* item_slot, int n_slots,
+                           int n_items, int n_tok, float* out, int heads, int dim, int vdim, int chunk, float* chunk_S, float* chunk_n,
+                           float* chunk_mb, int* status, cudaStream_t stream) {
     const int vblocks = (vdim + 31) / 32;
+    const int zb = (vblocks + NW - 1) / NW;
     if (chunk <= 0) {
-        launch(mlstm_recurrent_kernel<DMAX>, dim3(n_items, heads, vblocks), dim3(32), 0, stream, c, S, n, m, item_row_start, item_slot,
-               n_slots, out, heads, dim, vdim, status);
+        launch(mlstm_recurrent_kernel<DMAX, NW>, dim3(n_items, heads, zb), dim3(NW * 32), 0, stream, c, S, n, m, item_row_start, item_slot,
+               n_slots, out, heads, dim, vdim, vblocks, status);
         IMPARO_CHECK_LAUNCH();
         return 0;
     }
     const int most = n_tok / chunk + n_items;
-    launch(mlstm_chunk_kernel<DMAX, false>, dim3(most, heads, vblocks), dim3(32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
-           item_row_start, n_items, chunk, (float*)nullptr, heads, dim, vdim, item_slot, n_slots, m);
+    launch(mlstm_chunk_kernel<DMAX, NW, false>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
+           item_row_start, n_items, chunk, (float*)nullptr, heads, dim, vdim, vblocks, item_slot, n_slots, m);
     IMPARO_CHECK_LAUNCH();
     const int entries = dim * vdim + vblocks * dim;
     launch(mlstm_chunk_scan_kernel, dim3(n_items, heads, (entries + 255) / 256), dim3(256), 0, stream, chunk_S, chunk_n, chunk_mb, S, n,
            (const float*)m, item_row_start, item_slot, n_slots, chunk, heads, dim, vdim, vblocks, status);
     IMPARO_CHECK_LAUNCH();
-    launch(mlstm_chunk_kernel<DMAX, true>, dim3(most, heads, vblocks), dim3(32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
-           item_row_start, n_items, chunk, out, heads, dim, vdim, item_slot, n_slots, m);
+    launch(mlstm_chunk_kernel<DMAX, NW, true>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
+           item_row_start, n_items, chunk, out, heads, dim, vdim, vblocks, item_slot, n_slots, m);
     IMPARO_CHECK_LAUNCH();
     return 0;
+}
+
+// the warps of a CTA share the staged keys and queries: as many as the head has blocks of value columns, up to four
+template <int DMAX>
+static int mlstm_launch(const MlstmCols& c, float* S, float* n, float* m, const int* item_row_start, const int* item_slot, int n_slots,
+                        int n_items, int n_tok, float* out, int heads, int dim, int vdim, int chunk, float* chunk_S, float* chunk_n,
+                        float* chunk_mb, int* status, cudaStream_t stream) {
+    const int vblocks = (vdim + 31) / 32;
+    if (vblocks >= 3)
+        return mlstm_launch_nw<DMAX, 4>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                        chunk_S, chunk_n, chunk_mb, status, stream);
+    if (vblocks == 2)
+        return mlstm_launch_nw<DMAX, 2>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                        chunk_S, chunk_n, chunk_mb, status, stream);
+    return mlstm_launch_nw<DMAX, 1>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                    chunk_S, chunk_n, chunk_mb, status, stream);
 }
 
 // proj: float32 rows of `stride` floats with q and k (heads * dim each), v (heads * vdim) and the two gates' pre-activations
