@@ -12,7 +12,7 @@
 //      With a sink the running max starts at 0 and the running sum at 1: the extra term is a key
 //      of score 0 seen before all others; with sink values (one number per head) the extra term is exp(value) instead of 1:
 //      the running max starts at the head's value.  With a soft cap c the scaled score becomes c * tanh(score / c).
-//      Heads up to 512 wide (a cache of latent vectors that every head reads is one wide key/value head).
+//      Heads up to 640 wide (a cache of latent vectors that every head reads is one wide key/value head).
 //  (3) qkv_prepare_store: the same rows as a 32-bit product, for variants that work on whole heads in 32-bit before
 //      anything is rounded: biases added, half-split rotation, then q and k divided by their own root mean square
 //      per head (a norm without a weight), values optionally blended with the values another layer made for the
@@ -25,7 +25,7 @@ namespace imparo {
 
 constexpr int ANY_MAX_HEAD = 256;
 constexpr int ANY_WARPS = 4;
-constexpr int ANY_ATT_MAX_HEAD = 512;          // attention_any alone takes heads this wide
+constexpr int ANY_ATT_MAX_HEAD = 640;          // attention_any alone takes heads this wide
 
 template <typename T>
 __global__ void __launch_bounds__(ANY_WARPS * 32)

@@ -1189,7 +1189,7 @@ def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved
 
 def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale, sink,
                   out, nh, nkv, hd, vd, status, softcap: float = 0.0, sink_values: Optional[torch.Tensor] = None) -> None:
-    """General attention: any head size hd and value size vd up to 512, optional window, optional sink (one more
+    """General attention: any head size hd and value size vd up to 640, optional window, optional sink (one more
     term in the softmax's denominator that has no value: of score 0, or with sink_values, float32 [nh], of the head's
     own number, exp(value)), optional soft cap c > 0 on the scaled scores (c * tanh(score / c)).  out [T, nh*vd].
     k_cache and v_cache may be the same tensor (keys that are their own values)."""

@@ -29,8 +29,14 @@ def _matrix_memory(W, m, eps):
     return PartSpec("matrix_memory", {"hidden": W, "heads": m.heads, "dim": m.dim, "vdim": m.vdim, "gate_cap": m.gate_cap, "eps": eps})
 
 
-def zepesun_model_spec(cfg: ZepesunConfig) -> ModelSpec:
+def zepesun_model_spec(cfg: ZepesunConfig, tensor_shapes=None) -> ModelSpec:
+    """tensor_shapes: name -> shape of the model folder's tensors, when known: the position table has as many rows as the
+    stored tensor "pos" (which config.json's max_positions states too)."""
     W = cfg.width
+    n_positions = cfg.max_positions
+    if tensor_shapes is not None:
+        stored = tensor_shapes.get("pos")
+        n_positions = int(stored[0]) if stored else None
     layers = []
     for i, L in enumerate(cfg.layers):
         prefix = f"l{i}."
@@ -70,7 +76,7 @@ def zepesun_model_spec(cfg: ZepesunConfig) -> ModelSpec:
         layers.append(LayerSpec(prefix=prefix, mixer=mixer, feed_forward=ff,
                                 mixer_norm=PartSpec("rmsnorm", {"width": W, "eps": cfg.eps, "name": "norm1"}),
                                 feed_forward_norm=None, block="parallel_residual", params={"residual_scale": 1.0}))
-    positions = {"name": "pos", "rows": cfg.max_positions} if cfg.max_positions else None
+    positions = {"name": "pos", "rows": n_positions} if n_positions else None
     return ModelSpec(
         architecture="Zepesun", vocab_size=cfg.vocab, hidden_size=W,
         embedding=PartSpec("token_table", {"vocab": cfg.vocab, "width": W, "name": "embed", "scale": cfg.embedding_scale,
@@ -78,7 +84,7 @@ def zepesun_model_spec(cfg: ZepesunConfig) -> ModelSpec:
         layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
         final_norm=PartSpec("rmsnorm", {"width": W, "eps": cfg.eps, "name": "final.norm"}),
         head=PartSpec("linear", {"vocab": cfg.vocab, "width": W, "name": "head"}),
-        max_positions=cfg.max_positions or MAX_POSITIONS, eos_token_ids=())
+        max_positions=n_positions or MAX_POSITIONS, eos_token_ids=())
 
 
 register_architecture(Architecture(name="Zepesun", model_types=("zepesun",),

@@ -183,6 +183,19 @@ class AttentionMixer(Part):
     def adopt_input_weight(self, view) -> None:
         self.w_qkv = view
 
+    # with the 32-bit head preparation the first product [q | k | v | gate] is 32-bit: an arrangement that stacks several
+    # parts' matrices may make it (SideBySideMixer)
+    def wide_input_rows(self) -> int:
+        if not self.prepared or self.qk_conv is not None or self.v_share is not None:
+            return 0
+        return self.nh * self.hd + self.nkv * (self.hd + (0 if self.v_from_k else self.vd)) + (self.nh * self.vd if self.gate else 0)
+
+    def wide_input_weight(self):
+        return self.w_qkv
+
+    def adopt_wide_input_weight(self, view) -> None:
+        self.w_qkv = view
+
     def _forward_general(self, x, batch, kv, residual, accumulate, projected=None, conv_state=None):
         """Product (unless the arrangement made it), rotation + cache write, attention, output product."""
         rt, T = self.rt, x.shape[0]
@@ -198,8 +211,11 @@ class AttentionMixer(Part):
                 raise ValueError("attention: a layer that reads another entry's cache cannot prepare heads in 32-bit")
             # the product in 32-bit, so that biases, angles and the norm without a weight see unrounded heads
             wide = width + (nh * vd if self.gate else 0)          # the gate's pre-activations ride along, unrounded
-            qkv = rt.workspace.get("attn_qkv32", (T, wide), torch.float32, first="tokens")
-            ops.linear(x, self.w_qkv[:wide], qkv, status=rt.status)
+            if projected is not None and projected.dtype == torch.float32 and projected.shape[1] == wide:
+                qkv = projected
+            else:
+                qkv = rt.workspace.get("attn_qkv32", (T, wide), torch.float32, first="tokens")
+                ops.linear(x, self.w_qkv[:wide], qkv, status=rt.status)
             gate = qkv[:, width:] if self.gate else None
             if self.gate:
                 qkv = qkv[:, :width]

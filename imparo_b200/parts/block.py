@@ -126,8 +126,11 @@ class ParallelResidualBlock(Block):
         import inspect
         self._one_pass = (self.ff is not None and hasattr(self.ff, "forward_into")
                           and "extra" in inspect.signature(self.mixer.forward).parameters)
-        # a feed-forward whose forward() has an `accumulate` keyword may default to overwriting: here it adds
+        # a feed-forward whose forward() has an `accumulate` keyword may default to overwriting: here it adds, or (beside
+        # a mixer that takes the other sublayer's output along) writes a buffer that the mixer's one add carries in
         self._ff_adds = self.ff is not None and "accumulate" in inspect.signature(self.ff.forward).parameters
+        self._ff_rides = (self._ff_adds and not self._one_pass
+                          and "extra" in inspect.signature(self.mixer.forward).parameters)
 
     def weight_specs(self):
         return [w for p in self.parts for w in p.weight_specs()]
@@ -187,6 +190,11 @@ class ParallelResidualBlock(Block):
                 self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
             finally:
                 ops.disallow_deferred_add(x)
+            return None
+        if self._ff_rides and not probe:
+            y = self.rt.workspace.get("ffn_out", (x.shape[0], x.shape[1]), torch.float32, first="tokens")
+            self.ff.forward(h, batch, y, accumulate=False)
+            self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
             return None
         self.mixer.forward(h, batch, caches, x, **kw)
         kw.pop("projected", None)

@@ -62,8 +62,8 @@ class LatentAttention(Part):
         self.sink = bool(p.get("sink", False))
         self.gate = bool(p.get("gate", False))
         self.gate_per_head = p.get("gate") == "head"
-        if not 1 <= self.row <= 512:
-            raise ValueError(f"latent attention: cached row size {self.row} is not supported by the kernel (1 to 512)")
+        if not 1 <= self.row <= 640:
+            raise ValueError(f"latent attention: cached row size {self.row} is not supported by the kernel (1 to 640)")
         if max(self.dim, self.kv_rank) > 1536:
             raise ValueError("latent attention: head and latent sizes up to 1536")
         self.names = {k: prefix + v for k, v in {**self.NAMES, **p.get("names", {})}.items()}

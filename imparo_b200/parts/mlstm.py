@@ -70,15 +70,28 @@ class MatrixMemory(Part):
         vb = ops.mlstm_value_blocks(self.vdim)
         return (SlotState((self.heads, self.dim, self.vdim)), SlotState((self.heads, vb, self.dim)), SlotState((self.heads, vb)))
 
-    def forward(self, x, batch, caches, residual, accumulate=True):
+    # the 32-bit first product may be made by an arrangement that stacks several parts' matrices (SideBySideMixer)
+    def wide_input_rows(self) -> int:
+        return 2 * self.heads * self.dim + 2 * self.heads * self.vdim + 2 * self.heads
+
+    def wide_input_weight(self):
+        return self.w_in
+
+    def adopt_wide_input_weight(self, view) -> None:
+        self.w_in = view
+
+    def forward(self, x, batch, caches, residual, accumulate=True, projected=None):
         S, n, m = caches
         rt, T = self.rt, x.shape[0]
         ws = rt.workspace
         H = self.heads
         qk, vv = H * self.dim, H * self.vdim
         # the product stays 32-bit: gates, keys, values and queries enter the recurrence unrounded
-        proj = ws.get("mlstm_in", (T, self.w_in.shape[0]), torch.float32, first="tokens")
-        ops.linear(x, self.w_in, proj, status=rt.status)
+        if projected is not None:
+            proj = projected
+        else:
+            proj = ws.get("mlstm_in", (T, self.w_in.shape[0]), torch.float32, first="tokens")
+            ops.linear(x, self.w_in, proj, status=rt.status)
         o = ws.get("mlstm_o", (T, vv), torch.float32, first="tokens")
         chunk, scratch = 0, None
         if batch.max_tokens_per_item >= self.CHUNK_FROM:

@@ -10,6 +10,9 @@ added into the stream times `scale` (the arrangement's residual factor).  The br
 
 With `weights` (a factor per branch) the result is instead the plain weighted sum  out = sum_b weights[b] * branch_b(x),
 without norms (no norm tensors are read); the sum and the add are one kernel.
+
+Branches that all keep their first product in 32-bit (wide_input_rows() > 0: heads prepared in 32-bit, a recurrence that is
+fed unrounded rows) get it from ONE 32-bit product over the stacked matrices, made here.
 """
 from __future__ import annotations
 
@@ -90,12 +93,36 @@ class SideBySideMixer(Part):
         for (b, _), (at, n) in zip(self.branches, self._ranges()[0]):
             b.adopt_input_weight(view[at:at + n])
 
+    def _wide(self):
+        """(stacked matrix, column ranges) of the branches' 32-bit first products, when every branch has one."""
+        if getattr(self, "_wide_w", None) is None:
+            self._wide_w = False
+            subs = [b for b, _ in self.branches]
+            if len(subs) > 1 and all(getattr(b, "wide_input_rows", lambda: 0)() > 0 for b in subs):
+                ranges, at = [], 0
+                for b in subs:
+                    at = (at + 3) // 4 * 4
+                    ranges.append((at, b.wide_input_rows()))
+                    at += b.wide_input_rows()
+                first = subs[0].wide_input_weight()
+                w = torch.zeros((at, first.shape[1]), dtype=first.dtype, device=first.device)
+                for b, (a, n) in zip(subs, ranges):
+                    w[a:a + n] = b.wide_input_weight()
+                    b.adopt_wide_input_weight(w[a:a + n])
+                self._wide_w = (w, ranges)
+        return self._wide_w
+
     def forward(self, x, batch, caches, residual, scale: float = 1.0, extra=None, extra_scale: float = 0.0, projected=None):
         """extra: a float32 [tokens, hidden] buffer added as well, times extra_scale, in the same pass over the
         stream (the arrangement's other sublayer).  projected: the branches' first products, made by the arrangement."""
         rt, T = self.rt, x.shape[0]
         outs, at = [], 0
         ranges = self._ranges()[0] if projected is not None else None
+        wide = self._wide() if projected is None else False
+        if wide:
+            w, ranges = wide
+            projected = rt.workspace.get("branches_in32", (T, w.shape[0]), torch.float32, first="tokens")
+            ops.linear(x, w, projected, status=rt.status)
         for i, (b, _) in enumerate(self.branches):
             buf = rt.workspace.get(f"branch_out_{i}", (T, self.hidden), torch.float32, first="tokens")
             kw = {} if projected is None else {"projected": projected[:, ranges[i][0]:ranges[i][0] + ranges[i][1]]}

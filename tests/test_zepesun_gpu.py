@@ -392,7 +392,7 @@ def _latent_sizes(H, D, R, V, Cr, n_rot=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,R,V,Cr,n_rot", [(3, 16, 8, 12, 24, None), (5, 12, 12, 20, 28, 6), (6, 64, 32, 48, 128, None), (2, 24, 4, 8, 260, 2),
+@pytest.mark.parametrize("H,D,R,V,Cr,n_rot", [(3, 16, 8, 12, 24, None), (5, 12, 12, 20, 28, 6), (6, 64, 32, 48, 128, None), (2, 24, 4, 8, 260, 2), (2, 16, 64, 8, 512, 64),
                                               (1, 7, 0, 5, 9, None), (4, 8, 16, 8, 16, 16)])
 def test_latent_attention_kernels(dtype, H, D, R, V, Cr, n_rot):
     """The latent's norm, the rotation of the shared key part and of the queries' rotated parts, the cache write, queries
