@@ -95,10 +95,15 @@ class MatrixMemory(Part):
         o = ws.get("mlstm_o", (T, vv), torch.float32, first="tokens")
         chunk, scratch = 0, None
         if batch.max_tokens_per_item >= self.CHUNK_FROM:
-            # long portions: chunks of rows side by side; the chunk length is fixed, so the cut depends on the rows alone
-            chunk = self.CHUNK
-            most = T // chunk + batch.n_items
+            # long portions: chunks of rows side by side.  A chunk's CTA walks its rows one after the other, so the chunks are
+            # halved while they would leave SMs without a CTA (with several CTAs on an SM the walks share its issue slots
+            # and shorter chunks only add to the scan: 123 against 134 us per layer at 2,048 tokens, 8 heads); the length
+            # follows the step's totals alone (tokens, requests), which are part of its shape
             vb = ops.mlstm_value_blocks(self.vdim)
+            chunk = self.CHUNK
+            if (T // chunk + batch.n_items) * H * -(-vb // 4) < ops.sm_count():
+                chunk //= 2
+            most = T // chunk + batch.n_items
             scratch = (ws.get("mlstm_chunk_S", (most * H * self.dim * self.vdim,), torch.float32),
                        ws.get("mlstm_chunk_n", (most * H * vb * self.dim,), torch.float32),
                        ws.get("mlstm_chunk_mb", (most * H * vb * 3,), torch.float32))
