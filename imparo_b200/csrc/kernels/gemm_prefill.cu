@@ -55,6 +55,7 @@ struct Params {
     // the gated epilogue's activation (gated_act's kinds; 0: silu(gate) * up) and its limit
     int act;
     float limit;
+    const float* bias;       // the gated epilogue: [2N] = the gate product's bias, then the up product's; or null
 };
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -255,8 +256,17 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 for (int e = 0; e < 4; ++e) {
                                     const float g0 = __uint_as_float(gr[j + 2 * e]), g1 = __uint_as_float(gr[j + 2 * e + 1]);
                                     const float u0 = __uint_as_float(ur[j + 2 * e]), u1 = __uint_as_float(ur[j + 2 * e + 1]);
-                                    w[e] = p.act == 0 ? pack_bf16(silu_bf16(g0) * u0, silu_bf16(g1) * u1)
-                                                      : pack_bf16(gated_act_bf16(p.act, p.limit, g0, u0), gated_act_bf16(p.act, p.limit, g1, u1));
+                                    if (p.act == 0 && p.bias == nullptr) {
+                                        w[e] = pack_bf16(silu_bf16(g0) * u0, silu_bf16(g1) * u1);
+                                    } else {
+                                        float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
+                                        if (p.bias) {
+                                            b0 = p.bias[f + 2 * e]; b1 = p.bias[f + 2 * e + 1];
+                                            c0 = p.bias[p.N + f + 2 * e]; c1 = p.bias[p.N + f + 2 * e + 1];
+                                        }
+                                        w[e] = pack_bf16(gated_act_bf16(p.act, p.limit, g0 + b0, u0 + c0),
+                                                         gated_act_bf16(p.act, p.limit, g1 + b1, u1 + c1));
+                                    }
                                 }
                                 *reinterpret_cast<uint4*>(out + f) = make_uint4(w[0], w[1], w[2], w[3]);
                             }
@@ -372,12 +382,14 @@ using namespace imparo::tcp;
 
 // x: [T, K] bfloat16 with row stride ldx (elements), inside a buffer of x_rows_alloc rows.
 // w: [N, K] bfloat16 dense (SwiGLU: [2N, K], gate rows then up rows).  out: [T, ldo].
-// epilogue: 0 store bfloat16, 1 store float32, 2 add into float32, 3 SwiGLU (bfloat16 [T, N]).
+// epilogue: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated (bfloat16 [T, N]: act, limit: gated_act's kinds, 0 is
+// SwiGLU; bias: float32 [2N] added to the gate and up products before the activation, or null).
 // Refused (-23): K or ldx not a multiple of 8, operands not 16-byte aligned, N or ldo not a
 // multiple of 8 (4 for the float32 outputs), out not 16-byte aligned: the caller then takes the
 // library product.
 extern "C" int imparo_gemm_prefill(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
-                                   int T, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+                                   int T, int N, int K, int epilogue, int act, float limit, const float* bias, int* status,
+                                   cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return -23;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return -23;
@@ -395,6 +407,7 @@ extern "C" int imparo_gemm_prefill(const void* x, int ldx, int x_rows_alloc, con
     p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.kblocks = (K + BK - 1) / BK;
     p.m_tiles = (T + TM - 1) / TM;
     p.n_tiles = epilogue == SWIGLU_BF16 ? (N + 127) / 128 : (N + TN - 1) / TN;
+    p.act = act; p.limit = limit; p.bias = bias;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles > (1 << 30)) return -2;
     const int ctas = (int)(tiles < sm_count() ? tiles : sm_count());

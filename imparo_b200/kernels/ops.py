@@ -454,9 +454,11 @@ def prefill_tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swigl
             and out.data_ptr() % 16 == 0 and out.dtype in (torch.float32, torch.bfloat16))
 
 
-def gemm_prefill(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None) -> None:
+def gemm_prefill(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None,
+                 act: str = "silu", limit: float = 0.0, bias: Optional[torch.Tensor] = None) -> None:
     """The persistent tensor-core product for many tokens.  epilogue: EPI_STORE_BF16 | EPI_STORE_F32 |
-    EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU (w = [gate rows; up rows], out = silu(x gate^T) * (x up^T))."""
+    EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU (w = [gate rows; up rows], out = act(x gate^T + b_g, x up^T + b_u) with act one of
+    gated_act's kinds, "silu" by default, and bias float32 [2N] or None)."""
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     _need(epilogue in (EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU), "gemm_prefill: unknown epilogue")
     T, K = x.shape
@@ -472,8 +474,13 @@ def gemm_prefill(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
             status = _S.status_fallback[key] = new_status(x.device)
     rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
     rows_alloc = max(T, min(rows_alloc, 1 << 30))
+    if bias is not None:
+        _cuda(bias)
+        _need(epilogue == EPI_SWIGLU and bias.dtype == torch.float32 and bias.numel() == 2 * N and bias.is_contiguous(),
+              "gemm_prefill: bias float32 [2N] with the gated epilogue")
     _check(_lib.kernels().imparo_gemm_prefill(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K,
-                                              epilogue, _ptr(status), _stream()), "gemm_prefill")
+                                              epilogue, GATED_ACTIVATIONS[act], float(limit), _ptr(bias), _ptr(status), _stream()),
+           "gemm_prefill")
 
 
 def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
@@ -499,7 +506,11 @@ def linear_gated(x, w_gu: torch.Tensor, out: torch.Tensor, kind: str, limit: flo
                  status: Optional[torch.Tensor] = None, tmp=None) -> None:
     """out[T, F] = act(x gate^T + b_g, x up^T + b_u) with w_gu = [gate; up] ([2F, K]), bias float32 [2F] or None, for the
     gated activations of gated_act: the product into tmp [T, 2F] (a tensor, or a function that makes it), then one kernel
-    that adds the biases and applies the activation."""
+    that adds the biases and applies the activation.  For many bfloat16 tokens: the persistent tensor-core product with the
+    biases and the activation in its epilogue (one launch, no [T, 2F] tensor)."""
+    if prefill_tc_usable(x, w_gu, out, swiglu=True):
+        gemm_prefill(x, w_gu, out, EPI_SWIGLU, status, act=kind, limit=limit, bias=bias)
+        return
     if callable(tmp):
         tmp = tmp()
     _need(tmp is not None and tmp.shape == (x.shape[0], w_gu.shape[0]), "linear_gated: tmp [T, 2F] needed")

@@ -638,6 +638,30 @@ def test_small_kernels(dtype):
     assert np.abs(xd.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
 
 
+@pytest.mark.parametrize("T,width,F,kind,limit,biased", [(300, 128, 256, "gelu_tanh", 0.0, True), (700, 64, 136, "gelu_tanh", 0.0, False),
+                                                         (256, 320, 96, "clamped_swish", 1.0, False), (40, 128, 64, "gelu_tanh", 0.0, True)])
+def test_gated_product_with_biases(T, width, F, kind, limit, biased):
+    """The gate and up products with their biases and the activation: in the persistent tensor-core product's epilogue for
+    many bfloat16 rows, as a product and an activation kernel for few."""
+    import torch
+    from imparo_b200.kernels import ops
+    rng = np.random.default_rng(T + F)
+    x, w = _bf16_round(rng.standard_normal((T, width))), _bf16_round(rng.standard_normal((2 * F, width)) / np.sqrt(width) * 2.0)
+    bias = rng.standard_normal(2 * F) if biased else None
+    g, u = x @ w[:F].T + (bias[:F] if biased else 0.0), x @ w[F:].T + (bias[F:] if biased else 0.0)
+    if kind == "gelu_tanh":
+        want = P.gelu_tanh(g) * u
+    else:
+        gc = np.minimum(g, limit)
+        want = gc * P.sigmoid(1.702 * gc) * (np.clip(u, -limit, limit) + 1.0)
+    out = torch.empty(T, F, dtype=torch.bfloat16, device="cuda")
+    status = ops.new_status("cuda")
+    ops.linear_gated(_dev(x, torch.bfloat16), _dev(w, torch.bfloat16), out, kind, limit=limit, bias=None if bias is None else _f32(bias),
+                     status=status, tmp=lambda: torch.empty(T, 2 * F, dtype=torch.bfloat16, device="cuda"))
+    ops.read_status(status)
+    assert np.abs(out.float().cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()
+
+
 # ---- generation ------------------------------------------------------------------------------------------------
 
 def plain_generate(name, prompt, n_new):
