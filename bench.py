@@ -536,15 +536,15 @@ def zepesun_config(width, layers, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank
     the others routed (`experts` clamped experts of `ff` features in `groups` groups of which `keep` are candidates, `top` per
     token, and a shared one)."""
     lat = {"heads": lat_heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": lat_vdim, "kv_rank": kv_rank,
-           "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 250000.0, "dims": rot_dim}}
+           "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
     left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "mask": {"size": window}}
-    mem = {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": 15.0}
-    par = {"left": left, "right": mem, "left_scale": 1.2, "right_scale": 0.5}
-    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}},
-           "expert": {"ff": ff, "limit": 1.0}, "shared": {"ff": ff, "limit": 1.0}}
+    mem = {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": 10.0}
+    par = {"left": left, "right": mem, "left_scale": 1.0, "right_scale": 1.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}},
+           "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": ff, "limit": 7.0}}
     kinds = [("latent_attention", lat), ("parallel", par), ("mlstm", mem), ("mlstm", mem)]
-    return {"architecture": "Zepesun", "vocab": vocab, "width": width, "max_positions": positions, "norm": {"eps": 1e-6},
-            "embedding": {"scale": 3.0},
+    return {"architecture": "Zepesun", "vocab": vocab, "width": width, "max_positions": positions, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5},
             "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": top * ff} if i == 0 else moe}
                        for i in range(layers)]}
 

@@ -11,7 +11,8 @@
 //      (rank + rot wide; kr is one key part that all heads share); every head's plain query dimensions go to q_plain
 //      [T, heads * dim] and its rotated ones, turned by the position, to the last rot entries of the head's latent-space
 //      query q_lat [T, heads * (rank + rot)] (the first rank entries are U_k^T q_plain, made by heads_linear).  The turn: of the
-//      first n_rot of the rot dimensions, i pairs with i + n_rot/2, angle = position * inv_freq[i] in 32-bit.
+//      first n_rot of the rot dimensions, i pairs with i + n_rot/2, angle = position * inv_freq[i] in 32-bit.  Two CTAs per
+//      token: one for the queries, one for the cached row.
 //  (2) heads_linear: out[t, h, :] = W[h] x[t, h, :] for every head h (W [heads, out, in]), optionally times
 //      sigmoid(gate[t, h, :]) (a 32-bit product's columns).  A warp per output feature of a head and tile of eight rows;
 //      32-bit sums (for steps of few rows: many rows go to the library's batched product).
@@ -78,21 +79,24 @@ latent_rot_store_kernel(const float* __restrict__ proj, size_t stride, int heads
     pdl_wait();
     __syncthreads();
     const float* row = proj + (size_t)t * stride;
-    // queries: plain dimensions as they are, rotated ones turned
-    for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
-        const int h = i / dim, d = i % dim;
-        q_plain[(size_t)t * heads * dim + i] = from_f32<T>(row[(size_t)h * (dim + rot) + d]);
-    }
-    for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
-        const int h = i / rot, d = i % rot;
-        const float* qr = row + (size_t)h * (dim + rot) + dim;
-        float v = qr[d];
-        if (d < n_rot) {
-            const int j = d < half ? d : d - half;
-            const float sn = sn_s[j], cs = cs_s[j];
-            v = d < half ? qr[d] * cs - qr[d + half] * sn : qr[d] * cs + qr[d - half] * sn;
+    if (blockIdx.y == 0) {
+        // queries: plain dimensions as they are, rotated ones turned
+        for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+            const int h = i / dim, d = i % dim;
+            q_plain[(size_t)t * heads * dim + i] = from_f32<T>(row[(size_t)h * (dim + rot) + d]);
         }
-        q_lat[((size_t)t * heads + h) * row_w + rank + d] = from_f32<T>(v);
+        for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
+            const int h = i / rot, d = i % rot;
+            const float* qr = row + (size_t)h * (dim + rot) + dim;
+            float v = qr[d];
+            if (d < n_rot) {
+                const int j = d < half ? d : d - half;
+                const float sn = sn_s[j], cs = cs_s[j];
+                v = d < half ? qr[d] * cs - qr[d + half] * sn : qr[d] * cs + qr[d - half] * sn;
+            }
+            q_lat[((size_t)t * heads + h) * row_w + rank + d] = from_f32<T>(v);
+        }
+        return;
     }
     // the cached row
     const float* c = row + q_width;
@@ -222,11 +226,11 @@ extern "C" int imparo_latent_rot_store(const float* proj, long long stride, int 
     if (heads < 1 || dim < 1 || rot < 0 || rank < 1 || n_rot < 0 || n_rot > rot || n_rot > 512 || n_rot % 2 || (n_rot > 0 && inv_freq == nullptr)
         || stride < (long long)heads * (dim + rot) + rank + rot) return -2;
     if (dtype == IMPARO_DT_F32)
-        launch(latent_rot_store_kernel<float>, dim3(n_tok), dim3(128), 0, stream, proj, (size_t)stride, heads, dim, rot, rank, wc, eps,
+        launch(latent_rot_store_kernel<float>, dim3(n_tok, 2), dim3(128), 0, stream, proj, (size_t)stride, heads, dim, rot, rank, wc, eps,
                inv_freq, n_rot, positions, item_of_token, (float*)q_plain, (float*)q_lat, (float*)cache, table, max_blocks, page_size,
                n_pages, status);
     else if (dtype == IMPARO_DT_BF16)
-        launch(latent_rot_store_kernel<__nv_bfloat16>, dim3(n_tok), dim3(128), 0, stream, proj, (size_t)stride, heads, dim, rot, rank, wc,
+        launch(latent_rot_store_kernel<__nv_bfloat16>, dim3(n_tok, 2), dim3(128), 0, stream, proj, (size_t)stride, heads, dim, rot, rank, wc,
                eps, inv_freq, n_rot, positions, item_of_token, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_lat, (__nv_bfloat16*)cache,
                table, max_blocks, page_size, n_pages, status);
     else return -1;

@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(128)
 moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int parts, int top, int softmax_scores, int renormalise,
                 int groups, int keep, float renorm_eps, float weight_scale, int out_stride, int* __restrict__ ids,
                 float* __restrict__ wts) {
-    extern __shared__ __align__(16) float pick_smem[];   // [4][experts]
+    extern __shared__ __align__(16) float pick_smem[];   // [4][experts] scores, then [4][groups] maxima of the groups
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -162,26 +162,23 @@ moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int p
     // experts stay candidates (ties: the lower group).  The others leave the candidates; the softmax above counted them.
     if (groups > 1 && keep < groups) {
         const int per = experts / groups;
-        // lane g (and g + 32, ...) finds group g's maximum; a group is kept when fewer than `keep` groups beat it.  All
-        // verdicts first, then the masking, so that every verdict reads the scores as they were.
-        unsigned long long drop = 0ull;                   // bit i: this lane's group lane + 32 i leaves (groups <= 2048)
-        for (int g0 = 0, it = 0; g0 < groups; g0 += 32, ++it) {
-            const int g = g0 + lane;
-            if (g >= groups) continue;
-            float mine = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) mine = fmaxf(mine, s[e]);
-            int beaten = 0;
-            for (int o = 0; o < groups; ++o) {
-                float other = -INFINITY;
-                for (int e = o * per; e < (o + 1) * per; ++e) other = fmaxf(other, s[e]);
-                if (other > mine || (other == mine && o < g)) ++beaten;
-            }
-            if (beaten >= keep) drop |= 1ull << it;
+        // every group's maximum first (a lane per group), then a lane per group counts the groups that beat its own: a group
+        // is kept when fewer than `keep` do.  All verdicts are in before any score is masked.
+        float* gmax = pick_smem + (size_t)4 * experts + (size_t)warp * groups;
+        for (int g = lane; g < groups; g += 32) {
+            float mx = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) mx = fmaxf(mx, s[e]);
+            gmax[g] = mx;
         }
         __syncwarp();
-        for (int g0 = 0, it = 0; g0 < groups; g0 += 32, ++it) {
-            const int g = g0 + lane;
-            if (g < groups && ((drop >> it) & 1ull))
+        for (int g = lane; g < groups; g += 32) {
+            const float mine = gmax[g];
+            int beaten = 0;
+            for (int o = 0; o < groups; ++o) {
+                const float other = gmax[o];
+                if (other > mine || (other == mine && o < g)) ++beaten;
+            }
+            if (beaten >= keep)
                 for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -INFINITY;
         }
         __syncwarp();
@@ -632,7 +629,12 @@ using namespace imparo;
 // `keep` best groups' experts may be chosen; groups <= 1: all), renorm_eps (added to the chosen scores' sum before the
 // division when renormalise is set), weight_scale (a factor on the weights), out_stride (ids and wts have out_stride >= top
 // entries per row: the entries beyond `top` name experts every row uses with weight 1, numbered from `experts` on).
+static inline size_t pick_smem_bytes(int experts, int groups) {
+    return (size_t)4 * (experts + (groups > 1 ? groups : 0)) * sizeof(float);
+}
+
 static inline bool pick_args_ok(int experts, int top, int groups, int keep, int out_stride) {
+    if (pick_smem_bytes(experts, groups) > 48 * 1024) return false;
     if (top < 1 || top > experts || top > 32 || experts > 2048 || out_stride < top || out_stride > top + 32) return false;
     if (groups > 1 && (experts % groups != 0 || keep < 1 || keep > groups || keep * (experts / groups) < top)) return false;
     return true;
@@ -655,7 +657,7 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
                per, logits);
     else return -1;
     IMPARO_CHECK_LAUNCH();
-    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, (const float*)logits, n_rows,
+    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), pick_smem_bytes(experts, groups), stream, (const float*)logits, n_rows,
            experts, 1, top, softmax_scores, renormalise, groups, keep, renorm_eps, weight_scale, out_stride, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;
@@ -670,7 +672,7 @@ extern "C" int imparo_moe_pick(const float* logits, int n_rows, int experts, int
                                cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (!pick_args_ok(experts, top, groups, keep, out_stride) || parts < 1 || parts > 4) return -2;
-    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, logits, n_rows, experts,
+    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), pick_smem_bytes(experts, groups), stream, logits, n_rows, experts,
            parts, top, softmax_scores, renormalise, groups, keep, renorm_eps, weight_scale, out_stride, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -66,9 +66,13 @@ def make_requests(name, lengths, seed=0):
     return {f"r{i}": rng.integers(0, ALL[name]["vocab"], n).tolist() for i, n in enumerate(lengths)}
 
 
-_plain, _gaps = {}, {}
+_plain, _gaps, _cond = {}, {}, {}
 CLOSE_CALL = 0.03          # router decisions closer than this (in logits) may go the other way under 8-bit rounding
 AFTER = 3                  # and the mixers carry such a place's deviation on to the next few
+# A place where rounding is blown up: at a sequence's first tokens the matrix memory's read-out is sign(k . q) v / rms(v) after its
+# per-head norm, whatever the size of k . q, so a dot product near zero decides the whole head.  Such places show in the plain
+# implementation itself (32-bit against 64-bit): far above its usual rounding error there, they are not asked of bfloat16.
+ILL_CONDITIONED = 10.0     # times the request's median 32-bit error (and at least 1e-6 of the logits' scale)
 
 
 def plain_logits(name, requests, seed=1):
@@ -79,17 +83,24 @@ def plain_logits(name, requests, seed=1):
             gaps = []
             _plain[key] = P.forward(ALL[name], weights(name, seed), toks, gaps=gaps)
             _gaps[key] = np.min(np.stack(gaps), axis=0) if gaps else np.full(len(toks), np.inf)
+            single = P.forward(ALL[name], weights(name, seed), toks, dtype=np.float32)
+            _cond[key] = np.abs(single - _plain[key]).max(axis=1) / max(float(np.abs(_plain[key]).max()), 1e-30)
         out[rid] = _plain[key]
     return out
 
 
 def close_calls(name, requests, seed=1):
-    """(request, position) places at which a router decision of the plain implementation was a close call, and the places
-    right after each: bfloat16 may decide them the other way, and another expert's output is another vector altogether."""
+    """(request, position) places at which a router decision of the plain implementation was a close call or which blow
+    rounding up (ILL_CONDITIONED), and the places right after each: bfloat16 may decide them the other way, and another
+    expert's output (or a head with the other sign) is another vector altogether."""
     plain_logits(name, requests, seed)
     out = set()
     for rid, toks in requests.items():
-        for p in np.nonzero(_gaps[(name, seed, tuple(toks))] < CLOSE_CALL)[0]:
+        key = (name, seed, tuple(toks))
+        for p in np.nonzero(_gaps[key] < CLOSE_CALL)[0]:
+            out.update((rid, int(p) + k) for k in range(AFTER + 1))
+        cond = _cond[key]
+        for p in np.nonzero(cond > max(ILL_CONDITIONED * float(np.median(cond)), 1e-6))[0]:
             out.update((rid, int(p) + k) for k in range(AFTER + 1))
     return out
 
@@ -294,7 +305,7 @@ def _run_memory(rows, lens, cuts, slots, b_i, b_f, H, D, V, cap, n_slots=6, chun
 
 
 @pytest.mark.parametrize("chunk", [0, 64, 16])
-@pytest.mark.parametrize("H,D,V,cap", [(4, 32, 48, 12.0), (2, 16, 24, 6.0), (3, 8, 40, 10.0), (1, 40, 70, 3.0), (2, 136, 20, 20.0), (1, 7, 5, 2.0),
+@pytest.mark.parametrize("H,D,V,cap", [(4, 32, 40, 11.0), (2, 16, 24, 6.0), (3, 8, 40, 10.0), (1, 40, 70, 3.0), (2, 136, 20, 20.0), (1, 7, 5, 2.0),
                                        (2, 64, 64, 15.0), (1, 200, 33, 8.0)])
 def test_matrix_memory_kernels(H, D, V, cap, chunk):
     """Capped gates, the running maximum that starts at zero, the recurrence and the read-out on three requests of unequal
@@ -483,7 +494,7 @@ def _window_by_kernels(dtype, m, rows, bias, cuts, page, tensor_cores=False):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("nh,nkv,hd,vd,window", [(4, 2, 16, 16, 9), (6, 1, 8, 12, None), (3, 3, 24, 8, 70), (6, 2, 48, 48, 40), (2, 2, 12, 12, 1)])
+@pytest.mark.parametrize("nh,nkv,hd,vd,window", [(4, 2, 16, 16, 9), (6, 1, 8, 12, None), (3, 3, 24, 8, 70), (6, 3, 48, 48, 33), (2, 2, 12, 12, 1)])
 def test_gated_window_attention_kernels(dtype, nh, nkv, hd, vd, window):
     """Biases, no rotation, the window, grouped heads, a value size of its own and the gate per output element: a prompt of
     45 tokens, then 30 tokens one by one on the same cache (pages of 4: every border is crossed)."""
@@ -499,7 +510,7 @@ def test_gated_window_attention_kernels(dtype, nh, nkv, hd, vd, window):
 
 
 @pytest.mark.parametrize("dtype,hd,tensor_cores", [("float32", 32, False), ("bfloat16", 32, False), ("bfloat16", 64, True)])
-@pytest.mark.parametrize("size,page", [(16, 16), (17, 16), (33, 8), (5, 4), (64, 16), (40, 32)])
+@pytest.mark.parametrize("size,page", [(16, 16), (17, 16), (33, 8), (5, 4), (64, 16), (45, 32)])
 def test_a_key_just_inside_and_just_outside_the_window(dtype, hd, tensor_cores, size, page):
     """Marked keys before, at and after page borders score far above all others for queries that point their way.  The
     query `size - 1` positions after one still sees it and returns its marked value; the next query does not
@@ -514,7 +525,7 @@ def test_a_key_just_inside_and_just_outside_the_window(dtype, hd, tensor_cores, 
         assert np.abs(got[p + size, :hd] - 5.0).max() > 1.5
 
 
-@pytest.mark.parametrize("E,top,groups,keep,scale", [(16, 4, 4, 3, 2.0), (6, 2, 3, 2, 1.7), (8, 2, 2, 1, 1.0), (5, 5, 1, 1, 2.0), (3, 2, 3, 3, 3.0),
+@pytest.mark.parametrize("E,top,groups,keep,scale", [(16, 3, 4, 2, 1.5), (6, 2, 3, 2, 1.7), (8, 2, 2, 1, 1.0), (5, 5, 1, 1, 2.0), (3, 2, 3, 3, 3.0),
                                                      (64, 6, 8, 2, 1.0), (40, 3, 40, 5, 0.5)])
 def test_router_with_groups(E, top, groups, keep, scale):
     """Softmax scores over all experts, only the best groups' experts as candidates, the chosen scores renormalised and
@@ -542,7 +553,7 @@ def test_router_with_groups(E, top, groups, keep, scale):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,E,top,ff,width,limit,shared_ff", [(5, 6, 2, 24, 64, 1.5, 24), (40, 8, 3, 32, 128, 1.0, 64), (300, 8, 2, 64, 128, 1.0, 64),
-                                                               (70, 4, 1, 16, 52, 0.8, None), (150, 16, 4, 96, 320, 1.0, 96)])
+                                                               (70, 4, 1, 16, 52, 0.8, None), (150, 12, 3, 80, 256, 2.0, 80)])
 def test_clamped_experts_with_a_shared_one(dtype, T, E, top, ff, width, limit, shared_ff):
     """The routed feed-forward as a part: clamped experts pair by pair, sorted into small tiles and on the tensor-memory
     product, with a shared expert of the experts' size (stacked behind them), of another size (a pass of its own) or none."""
@@ -639,7 +650,7 @@ def test_small_kernels(dtype):
 
 
 @pytest.mark.parametrize("T,width,F,kind,limit,biased", [(300, 128, 256, "gelu_tanh", 0.0, True), (700, 64, 136, "gelu_tanh", 0.0, False),
-                                                         (256, 320, 96, "clamped_swish", 1.0, False), (40, 128, 64, "gelu_tanh", 0.0, True)])
+                                                         (256, 192, 80, "clamped_swish", 2.0, False), (40, 128, 64, "gelu_tanh", 0.0, True)])
 def test_gated_product_with_biases(T, width, F, kind, limit, biased):
     """The gate and up products with their biases and the activation: in the persistent tensor-core product's epilogue for
     many bfloat16 rows, as a product and an activation kernel for few."""

@@ -131,7 +131,7 @@ def test_configuration_reads_every_size_and_names_what_is_wrong():
     arch, cfg = load_config(ALL["B"])
     assert arch.name == "Zepesun" and cfg.width == 52 and cfg.embedding_scale == 1.0 and cfg.max_positions == 900
     lat = cfg.layers[1].mixer
-    assert (lat.heads, lat.dim, lat.rot_dim, lat.rot_dims, lat.kv_rank, lat.rot_base) == (5, 12, 12, 6, 28, 250000.0)
+    assert (lat.heads, lat.dim, lat.rot_dim, lat.rot_dims, lat.kv_rank, lat.rot_base) == (5, 12, 12, 6, 28, 500000.0)
     par = cfg.layers[3].mixer
     assert par.left.window is None and par.left.kv_heads == 1 and par.right.gate_cap == 12.0 and cfg.layers[2].mlp is None
     moe = cfg.layers[1].mlp

@@ -34,7 +34,7 @@ def draw_config(seed, fast=False):
             rank, rot_dim = pick([(64, 0), (48, 16), (32, 32), (128, 0), (96, 32), (64, 64), (120, 8)])
         m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": float(rng.uniform(0.05, 0.4))}
         if rot_dim:
-            m["rot"] = {"base": float(pick([50.0, 10000.0, 250000.0])), "dims": 2 * int(rng.integers(1, rot_dim // 2 + 1)) if rng.random() < 0.4 else rot_dim}
+            m["rot"] = {"base": float(pick([50.0, 10000.0, 500000.0])), "dims": 2 * int(rng.integers(1, rot_dim // 2 + 1)) if rng.random() < 0.4 else rot_dim}
         return {"type": "latent_attention", "mixer": m}
 
     def window():
@@ -48,12 +48,12 @@ def draw_config(seed, fast=False):
             dim = vdim = pick([64, 128])
         m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": float(rng.uniform(0.05, 0.4))}
         if rng.random() < 0.85:
-            m["mask"] = {"size": int(pick([1, 2, 5, 16, 17, 31, 40, 64, 100, 300]))}
+            m["mask"] = {"size": int(pick([1, 2, 5, 16, 17, 31, 45, 64, 100, 300]))}
         return m
 
     def memory():
         return {"heads": pick([1, 2, 3, 4, 6]), "dim": pick([4, 7, 8, 16, 24, 32, 64, 100, 128, 200]),
-                "vdim": pick([4, 8, 12, 20, 32, 33, 48, 64, 70, 128]), "gate_cap": float(pick([2.0, 8.0, 12.0, 15.0, 30.0]))}
+                "vdim": pick([4, 8, 12, 20, 32, 33, 48, 64, 70, 128]), "gate_cap": float(pick([2.0, 8.0, 11.0, 14.0, 30.0]))}
 
     def mlp():
         r = rng.random()
@@ -82,8 +82,8 @@ def draw_config(seed, fast=False):
         if kind == "latent":
             L = latent()
         elif kind == "parallel":
-            L = {"type": "parallel", "mixer": {"left": window(), "right": memory(), "left_scale": float(pick([1.0, 1.2, 0.4])),
-                                               "right_scale": float(pick([1.0, 0.5, 1.5]))}}
+            L = {"type": "parallel", "mixer": {"left": window(), "right": memory(), "left_scale": float(pick([1.0, 1.3, 0.4])),
+                                               "right_scale": float(pick([1.0, 0.6, 1.5]))}}
         else:
             L = {"type": "mlstm", "mixer": memory()}
         L["mlp"] = mlp()

@@ -64,17 +64,17 @@ ZEP_B = {
     "architecture": "Zepesun", "vocab": 301, "width": 52, "max_positions": 900, "norm": {"eps": 1e-6},
     "layers": [
         with_mlp(mlstm(2, 24, 33, 15.0), dense(30)),
-        with_mlp(latent(5, 12, 12, 20, 28, 0.2, rot_dims=6, base=250000.0), moe(5, 5, 12, 1.0, 2.0)),
+        with_mlp(latent(5, 12, 12, 20, 28, 0.2, rot_dims=6, base=500000.0), moe(5, 5, 12, 1.0, 2.0)),
         with_mlp(parallel(window(3, 3, 24, 8, 0.2, size=70), memory(4, 12, 8, 3.0), 0.7, 1.1), None),
         with_mlp(parallel(window(6, 1, 8, 12, 0.35), memory(1, 40, 70, 12.0), 1.0, 1.0), dense(64)),
     ]}
 
 ZEP_C = {
-    "architecture": "Zepesun", "vocab": 640, "width": 128, "max_positions": 1200, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.0},
+    "architecture": "Zepesun", "vocab": 512, "width": 128, "max_positions": 1200, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.5},
     "layers": [
-        with_mlp(parallel(window(4, 2, 64, 64, 0.125, size=40), memory(2, 64, 64, 12.0), 1.2, 0.5), moe(8, 2, 64, 1.0, 2.0, groups=(2, 1), shared=(64, 1.0))),
+        with_mlp(parallel(window(4, 2, 64, 64, 0.125, size=48), memory(2, 64, 64, 9.0), 1.1, 0.7), moe(8, 2, 64, 1.5, 1.5, groups=(2, 1), shared=(64, 1.5))),
         with_mlp(latent(4, 32, 16, 32, 48, 0.14, base=10000.0), dense(128)),
-        with_mlp(mlstm(2, 32, 64, 15.0), moe(8, 3, 32, 2.0, 1.0, groups=(4, 3))),
+        with_mlp(mlstm(2, 32, 64, 14.0), moe(8, 3, 32, 2.0, 1.0, groups=(4, 3))),
     ]}
 
 ZEP_D = {
