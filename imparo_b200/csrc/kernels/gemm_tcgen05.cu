@@ -59,6 +59,11 @@ struct Params {
     const float* cb_acc;         // [T, heads, splits, hd]
     const float* cb_ml;          // [T, heads, splits, 2]  (max, sum)
     int cb_splits, cb_hd, cb_heads;
+    // the gated epilogue: the activation (gated_act's kinds; 0: silu(gate) * up), its limit, and the gate and up products'
+    // biases ([2N] float32, or null)
+    int act;
+    float limit;
+    const float* bias;
 };
 
 __device__ __forceinline__ uint4 pack8(const float* v) {
@@ -326,8 +331,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
 #pragma unroll
                         for (int j = 0; j < 16; j += 2) {
                             const int t = t0 + c + 16 * u + j + parity;
-                            if (t < p.T)
-                                out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_bf16(ex[ff * 17 + j + parity]) * ex[(64 + ff) * 17 + j + parity]);
+                            if (t < p.T) {
+                                const float g = ex[ff * 17 + j + parity], u = ex[(64 + ff) * 17 + j + parity];
+                                float r;
+                                if (p.act == 0 && p.bias == nullptr) r = silu_bf16(g) * u;
+                                else r = gated_act_bf16(p.act, p.limit, g + (p.bias ? p.bias[f] : 0.f), u + (p.bias ? p.bias[p.N + f] : 0.f));
+                                out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
+                            }
                         }
                     }
                 }
@@ -640,9 +650,9 @@ static int partials_map(float* scratch, int T, int N, int splits, int nt, Params
 // x: [T, K] bfloat16 with row stride ldx (elements), inside a buffer of x_rows_alloc rows.
 // w: [N, K] bfloat16 dense (SwiGLU: [2N, K], gate rows then up rows).  out: [T, ldo].
 // scratch / counters: from imparo_gemm_tc_plan; counters must be zero (they are left zero).
-extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
-                              int T, int N, int K, int epilogue, float* scratch, int* counters, int* status,
-                              cudaStream_t stream) {
+static int gemm_tc_impl(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
+                        int T, int N, int K, int epilogue, float* scratch, int* counters, int* status,
+                        int act, float limit, const float* bias, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return -23;                   // TMA: 16-byte rows
     if (((uintptr_t)x | (uintptr_t)w) & 15) return -23;
@@ -658,6 +668,7 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
     Params p = {};
     p.out = out; p.scratch = scratch; p.counters = counters; p.status = status;
     p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
+    p.act = act; p.limit = limit; p.bias = bias;
     const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
     dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
     if (grid.y > 65535) return -2;
@@ -674,6 +685,22 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
             return launch_nt<PARTIAL_F32>(nt, mw, mx, mo, p, grid, stream);
     }
     return -22;
+}
+
+
+extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
+                              int T, int N, int K, int epilogue, float* scratch, int* counters, int* status,
+                              cudaStream_t stream) {
+    return gemm_tc_impl(x, ldx, x_rows_alloc, w, out, ldo, T, N, K, epilogue, scratch, counters, status, 0, 0.f, nullptr, stream);
+}
+
+// The gated epilogue (epilogue 3) with any of gated_act's activations and the two products' biases: out [T, N] bfloat16 =
+// act(x gate^T + bias[:N], x up^T + bias[N:]), w = [gate rows; up rows].
+extern "C" int imparo_gemm_tc_gated(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
+                                    int T, int N, int K, int act, float limit, const float* bias, float* scratch, int* counters,
+                                    int* status, cudaStream_t stream) {
+    if (act < 0 || act > 2) return -22;
+    return gemm_tc_impl(x, ldx, x_rows_alloc, w, out, ldo, T, N, K, SWIGLU_BF16, scratch, counters, status, act, limit, bias, stream);
 }
 
 

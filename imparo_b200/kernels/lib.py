@@ -79,6 +79,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gemm_tc_plan", [I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int)])
     _declare(lib, "imparo_gemm_tc_max_clusters", [I, I])
     _declare(lib, "imparo_gemm_tc", [P, I, I, P, P, I, I, I, I, I, P, P, P, S])
+    _declare(lib, "imparo_gemm_tc_gated", [P, I, I, P, P, I, I, I, I, I, c_float, P, P, P, P, S])
     _declare(lib, "imparo_gemm_tc_combine", [P, P, I, I, I, P, P, I, I, I, I, I, P, P, S])
     _declare(lib, "imparo_gemm_prefill", [P, I, I, P, P, I, I, I, I, I, I, c_float, P, P, S])
     _declare(lib, "imparo_qk_norm_rope_store",

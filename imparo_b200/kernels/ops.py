@@ -398,10 +398,11 @@ def tc_usable(x: torch.Tensor, w: torch.Tensor, any_size: bool = False) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None,
-            scratch: Optional[torch.Tensor] = None) -> None:
+            scratch: Optional[torch.Tensor] = None, act: str = "silu", limit: float = 0.0, bias: Optional[torch.Tensor] = None) -> None:
     """The hand-written tensor-core product (csrc/kernels/gemm_tcgen05.cu).
     epilogue: EPI_STORE_BF16 | EPI_STORE_F32 | EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU
-    (w = [gate rows; up rows] of shape [2F, K], out = silu(x gate^T) * (x up^T), [T, F])."""
+    (w = [gate rows; up rows] of shape [2F, K], out = act(x gate^T + b_g, x up^T + b_u), [T, F]; act one of gated_act's kinds,
+    "silu" by default; bias float32 [2F] or None)."""
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     _need(tc_usable(x, w, any_size=True), "gemm_tc: bfloat16 operands, K a multiple of 8, 16-byte aligned rows")
     T, K = x.shape
@@ -425,6 +426,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
             status = _S.status_fallback[key] = new_status(x.device)
     rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
     rows_alloc = max(T, min(rows_alloc, 1 << 30))
+    if epilogue == EPI_SWIGLU and (act != "silu" or bias is not None):
+        if bias is not None:
+            _cuda(bias)
+            _need(bias.dtype == torch.float32 and bias.numel() == 2 * N and bias.is_contiguous(), "gemm_tc: bias float32 [2N]")
+        _check(_lib.kernels().imparo_gemm_tc_gated(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K,
+                                                   GATED_ACTIVATIONS[act], float(limit), _ptr(bias), _ptr(scratch), _ptr(cnt),
+                                                   _ptr(status), _stream()), "gemm_tc_gated")
+        return
     _check(_lib.kernels().imparo_gemm_tc(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K, epilogue,
                                          _ptr(scratch), _ptr(cnt), _ptr(status), _stream()), "gemm_tc")
 
@@ -507,7 +516,11 @@ def linear_gated(x, w_gu: torch.Tensor, out: torch.Tensor, kind: str, limit: flo
     """out[T, F] = act(x gate^T + b_g, x up^T + b_u) with w_gu = [gate; up] ([2F, K]), bias float32 [2F] or None, for the
     gated activations of gated_act: the product into tmp [T, 2F] (a tensor, or a function that makes it), then one kernel
     that adds the biases and applies the activation.  For many bfloat16 tokens: the persistent tensor-core product with the
-    biases and the activation in its epilogue (one launch, no [T, 2F] tensor)."""
+    biases and the activation in its epilogue (one launch, no [T, 2F] tensor); for few: the weight-streaming tensor-core
+    product with the same epilogue."""
+    if x.dtype == torch.bfloat16 and gemm_backend() == "tcgen05" and tc_usable(x, w_gu):
+        gemm_tc(x, w_gu, out, EPI_SWIGLU, status, act=kind, limit=limit, bias=bias)
+        return
     if prefill_tc_usable(x, w_gu, out, swiglu=True):
         gemm_prefill(x, w_gu, out, EPI_SWIGLU, status, act=kind, limit=limit, bias=bias)
         return

@@ -61,6 +61,8 @@ class SideBySideMixer(Part):
             b.bind(tensors)
             if self.weights is None:
                 self.norm_w.append(tensors[norm_name])
+        self._wide_w = None
+        self._wide()                  # the stacked matrix is made now, not at a first step (which may be recorded as a graph)
 
     def cache_specs(self):
         return tuple(s for b, _ in self.branches for s in b.cache_specs())
