@@ -107,7 +107,7 @@ __device__ __forceinline__ float gated_act(int kind, float limit, float g, float
         return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     return silu(g) * u;
 }
-// The same for results that are rounded to bfloat16 at once (approximate exponential, division and tanh).
+// The same for results that are rounded to bfloat16 at once (approximate exponential and division).
 __device__ __forceinline__ float gated_act_bf16(int kind, float limit, float g, float u) {
     if (kind == IMPARO_GATED_CLAMPED) {
         g = fminf(g, limit);
@@ -115,9 +115,9 @@ __device__ __forceinline__ float gated_act_bf16(int kind, float limit, float g, 
         return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
     }
     if (kind == IMPARO_GATED_GELU_TANH) {
-        float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-        return 0.5f * g * (1.0f + t) * u;
+        // 0.5 (1 + tanh z) = 1 / (1 + exp(-2z)): no cancellation where tanh z is near -1
+        const float z2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+        return __fdividef(g, 1.0f + __expf(-z2)) * u;
     }
     return silu_bf16(g) * u;
 }

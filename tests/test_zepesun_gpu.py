@@ -306,7 +306,7 @@ def _run_memory(rows, lens, cuts, slots, b_i, b_f, H, D, V, cap, n_slots=6, chun
 
 @pytest.mark.parametrize("chunk", [0, 64, 16])
 @pytest.mark.parametrize("H,D,V,cap", [(4, 32, 40, 11.0), (2, 16, 24, 6.0), (3, 8, 40, 10.0), (1, 40, 70, 3.0), (2, 136, 20, 20.0), (1, 7, 5, 2.0),
-                                       (2, 64, 64, 15.0), (1, 200, 33, 8.0)])
+                                       (2, 64, 64, 15.0), (1, 200, 33, 8.0), (2, 16, 200, 5.0), (1, 72, 264, 9.0)])
 def test_matrix_memory_kernels(H, D, V, cap, chunk):
     """Capped gates, the running maximum that starts at zero, the recurrence and the read-out on three requests of unequal
     length: a launch of portions, then their next portions and single tokens from the states the launches before left
