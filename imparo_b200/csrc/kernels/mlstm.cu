@@ -16,8 +16,9 @@
 //      one column of S in registers (dim values); n is spread over the lanes (entry d with lane d % 32) and m is kept by
 //      every lane; the rows' k, q, v and gate inputs are copied asynchronously into shared memory a stage of 8 or 16 rows
 //      ahead, k and q once for the CTA's warps.  Every warp of a head repeats n and m and keeps a copy of its own in the
-//      slot (n is [heads, vblocks, dim], m [heads, vblocks], vblocks = ceil(vdim / 32)): no warp reads what another one
-//      writes.
+//      slot (n is [heads, vblocks, dim], m [heads, vblocks], vblocks = ceil(vdim / 32)): no CTA reads what another one
+//      writes.  Key sizes above 64: two lanes share a value column, each with half of the key dimension, so that a lane
+//      keeps at most 128 state entries in registers; a warp then owns 16 columns and two warps of a CTA share a copy.
 //  (2) long portions in chunks of `chunk` rows that run side by side, in three launches.  With b_t the sum of the log
 //      forget gates from the chunk's first row to row t, the recurrence unrolls to
 //          m_t = max(b_t + m_in, max_(s<=t) (b_t - b_s + a_s))
@@ -68,13 +69,16 @@ template <int N> __device__ __forceinline__ void ml_cp_wait() { asm volatile("cp
 // Rows [r_begin, r_end) of one request and head.  S: this lane's column of the state; nl: this lane's entries of n
 // (d = lane, lane + 32, ...); m: the running maximum (-INFINITY: an empty state).  OUT: the rows' outputs are wanted (else
 // only the state, and q is not read).  Every thread of the CTA calls this with the same rows; `live`: this lane has a column.
-template <int DMAX, int NW, bool OUT>
-__device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm, float (&S)[DMAX], float (&nl)[DMAX / 32], float& m,
+template <int DMAX, int NW, int SPLIT, bool OUT>
+__device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm, float (&S)[DMAX / SPLIT], float (&nl)[DMAX / 32], float& m,
                                         int r_begin, int r_end, float* __restrict__ out, int h, int heads, int dim, int vdim,
                                         int v0, int col, bool live, float* total_f) {
     constexpr int ST = MlSmem<DMAX, NW>::ST;
+    constexpr int DL = DMAX / SPLIT;                   // state entries per lane
+    constexpr int WCOLS = 32 / SPLIT;                  // value columns per warp
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = NW * 32;
-    const int vcols = min(NW * 32, vdim - v0);
+    const int dofs = (lane / WCOLS) * DL;              // this lane's stretch of the key dimension
+    const int vcols = min(NW * WCOLS, vdim - v0);
     // columns no copy writes: zero once
     for (int i = tid; i < 2 * ST * DMAX; i += nthreads) {
         const int d = i % DMAX;
@@ -127,17 +131,17 @@ __device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm
             const float keep = expf(f + m - m_new);       // an empty state (m = -inf) keeps nothing: exp(-inf) = 0
             const float put = expf(a - m_new);
             m = m_new;
-            const float pv = put * sm.v[buf][r][warp * 32 + lane];
+            const float pv = put * sm.v[buf][r][warp * WCOLS + (lane % WCOLS)];
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, nq = 0.f;
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&sm.k[buf][r][d]);
+            for (int d = 0; d < DL; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&sm.k[buf][r][dofs + d]);
                 S[d] = keep * S[d] + k4.x * pv;
                 S[d + 1] = keep * S[d + 1] + k4.y * pv;
                 S[d + 2] = keep * S[d + 2] + k4.z * pv;
                 S[d + 3] = keep * S[d + 3] + k4.w * pv;
                 if (OUT) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(&sm.q[buf][r][d]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&sm.q[buf][r][dofs + d]);
                     o0 += S[d] * q4.x; o1 += S[d + 1] * q4.y; o2 += S[d + 2] * q4.z; o3 += S[d + 3] * q4.w;
                 }
             }
@@ -149,7 +153,9 @@ __device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm
             if (OUT) {
                 nq = warp_sum(nq) * c.q_scale;
                 const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
-                if (live) out[(size_t)(base + r) * ((size_t)heads * vdim) + (size_t)h * vdim + col] = ((o0 + o1) + (o2 + o3)) * c.q_scale / den;
+                float o = (o0 + o1) + (o2 + o3);
+                if (SPLIT == 2) o += __shfl_xor_sync(0xffffffffu, o, 16);        // the other half of the key dimension
+                if (live && lane < WCOLS) out[(size_t)(base + r) * ((size_t)heads * vdim) + (size_t)h * vdim + col] = o * c.q_scale / den;
             }
         }
         __syncthreads();          // the stage after the next one is copied into this buffer
@@ -157,15 +163,19 @@ __device__ __forceinline__ void ml_walk(const MlstmCols& c, MlSmem<DMAX, NW>& sm
     if (total_f) *total_f = fsum;
 }
 
-template <int DMAX, int NW>
+// SPLIT = 2 (key sizes above 64): two lanes share a value column, each with half of the key dimension in registers; a warp
+// then owns 16 value columns and a CTA 16 * NW.
+template <int DMAX, int NW, int SPLIT>
 __global__ void __launch_bounds__(NW * 32)
 mlstm_recurrent_kernel(MlstmCols c, float* __restrict__ state_S, float* __restrict__ state_n, float* __restrict__ state_m,
                        const int* __restrict__ item_row_start, const int* __restrict__ item_slot, int n_slots,
                        float* __restrict__ out, int heads, int dim, int vdim, int vblocks, int* status) {
     __shared__ __align__(16) MlSmem<DMAX, NW> sm;
     pdl_trigger();
+    constexpr int DL = DMAX / SPLIT, WCOLS = 32 / SPLIT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int item = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * 32, vb = blockIdx.z * NW + warp, col = v0 + warp * 32 + lane;
+    const int item = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * WCOLS, wcol = v0 + warp * WCOLS, col = wcol + (lane % WCOLS);
+    const int vb = wcol / 32, dofs = (lane / WCOLS) * DL;
     const int r0 = item_row_start[item], r1 = item_row_start[item + 1];
     const int slot = item_slot[item];
     pdl_wait();
@@ -173,22 +183,23 @@ mlstm_recurrent_kernel(MlstmCols c, float* __restrict__ state_S, float* __restri
         if (threadIdx.x == 0) report(status, IMPARO_ST_SLOT_RANGE, 81, item, slot);
         return;
     }
-    const bool live = col < vdim, mine = vb < vblocks;
+    const bool live = col < vdim, mine = wcol < vdim;
     float* sp = state_S + (((size_t)slot * heads + h) * dim) * vdim + col;
     const size_t copy = ((size_t)slot * heads + h) * vblocks + (mine ? vb : 0);
     float* np = state_n + copy * dim;
     float* mp = state_m + copy;
-    float S[DMAX], nl[DMAX / 32];
+    float S[DL], nl[DMAX / 32];
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = (live && d < dim) ? sp[(size_t)d * vdim] : 0.f;
+    for (int d = 0; d < DL; ++d) S[d] = (live && dofs + d < dim) ? sp[(size_t)(dofs + d) * vdim] : 0.f;
 #pragma unroll
     for (int j = 0; j < DMAX / 32; ++j) nl[j] = (j * 32 + lane < dim) ? np[j * 32 + lane] : 0.f;
     float m = *mp;
-    ml_walk<DMAX, NW, true>(c, sm, S, nl, m, r0, r1, out, h, heads, dim, vdim, v0, col, live, nullptr);
+    ml_walk<DMAX, NW, SPLIT, true>(c, sm, S, nl, m, r0, r1, out, h, heads, dim, vdim, v0, col, live, nullptr);
     if (live) {
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d) if (d < dim) sp[(size_t)d * vdim] = S[d];
+        for (int d = 0; d < DL; ++d) if (dofs + d < dim) sp[(size_t)(dofs + d) * vdim] = S[d];
     }
+    __syncthreads();          // warps that share a copy of n and m have all read it
     if (mine) {
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) if (j * 32 + lane < dim) np[j * 32 + lane] = nl[j];
@@ -220,33 +231,35 @@ __device__ __forceinline__ bool ml_find_chunk(const int* __restrict__ item_row_s
 // chunk_S [chunks, heads, dim, vdim], chunk_n [chunks, heads, vblocks, dim], chunk_mb [chunks, heads, vblocks, 3] = (the
 // chunk's own maximum, its total b, the maximum it starts from).  The out pass of a request's last chunk leaves the slot's
 // maximum.
-template <int DMAX, int NW, bool OUT>
+template <int DMAX, int NW, int SPLIT, bool OUT>
 __global__ void __launch_bounds__(NW * 32)
 mlstm_chunk_kernel(MlstmCols c, float* __restrict__ chunk_S, float* __restrict__ chunk_n, float* __restrict__ chunk_mb,
                    const int* __restrict__ item_row_start, int n_items, int chunk, float* __restrict__ out, int heads, int dim,
                    int vdim, int vblocks, const int* __restrict__ item_slot, int n_slots, float* __restrict__ state_m) {
     __shared__ __align__(16) MlSmem<DMAX, NW> sm;
     pdl_trigger();
+    constexpr int DL = DMAX / SPLIT, WCOLS = 32 / SPLIT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * 32, vb = blockIdx.z * NW + warp, col = v0 + warp * 32 + lane;
+    const int g = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * NW * WCOLS, wcol = v0 + warp * WCOLS, col = wcol + (lane % WCOLS);
+    const int vb = wcol / 32, dofs = (lane / WCOLS) * DL;
     int item, r_begin, r_end, first;
     const bool found = ml_find_chunk(item_row_start, n_items, chunk, g, item, r_begin, r_end, first);
     pdl_wait();
     if (!found) return;
-    const bool live = col < vdim, mine = vb < vblocks;
+    const bool live = col < vdim, mine = wcol < vdim;
     float* sp = chunk_S + (((size_t)g * heads + h) * dim) * vdim + col;
     const size_t copy = ((size_t)g * heads + h) * vblocks + (mine ? vb : 0);
     float* np = chunk_n + copy * dim;
     float* mb = chunk_mb + copy * 3;
-    float S[DMAX], nl[DMAX / 32];
+    float S[DL], nl[DMAX / 32];
     float m, total;
     if (OUT) {                  // from the state the scan left for this chunk
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d) S[d] = (live && d < dim) ? sp[(size_t)d * vdim] : 0.f;
+        for (int d = 0; d < DL; ++d) S[d] = (live && dofs + d < dim) ? sp[(size_t)(dofs + d) * vdim] : 0.f;
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) nl[j] = (j * 32 + lane < dim) ? np[j * 32 + lane] : 0.f;
         m = mb[2];
-        ml_walk<DMAX, NW, true>(c, sm, S, nl, m, r_begin, r_end, out, h, heads, dim, vdim, v0, col, live, nullptr);
+        ml_walk<DMAX, NW, SPLIT, true>(c, sm, S, nl, m, r_begin, r_end, out, h, heads, dim, vdim, v0, col, live, nullptr);
         if (mine && lane == 0 && r_end == item_row_start[item + 1]) {
             const int slot = item_slot[item];
             if (slot >= 0 && slot < n_slots) state_m[((size_t)slot * heads + h) * vblocks + vb] = m;
@@ -254,14 +267,14 @@ mlstm_chunk_kernel(MlstmCols c, float* __restrict__ chunk_S, float* __restrict__
         return;
     }
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = 0.f;
+    for (int d = 0; d < DL; ++d) S[d] = 0.f;
 #pragma unroll
     for (int j = 0; j < DMAX / 32; ++j) nl[j] = 0.f;
     m = -INFINITY;
-    ml_walk<DMAX, NW, false>(c, sm, S, nl, m, r_begin, r_end, nullptr, h, heads, dim, vdim, v0, col, live, &total);
+    ml_walk<DMAX, NW, SPLIT, false>(c, sm, S, nl, m, r_begin, r_end, nullptr, h, heads, dim, vdim, v0, col, live, &total);
     if (live) {
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d) if (d < dim) sp[(size_t)d * vdim] = S[d];
+        for (int d = 0; d < DL; ++d) if (dofs + d < dim) sp[(size_t)(dofs + d) * vdim] = S[d];
     }
     if (mine) {
 #pragma unroll
@@ -328,46 +341,48 @@ mlstm_chunk_scan_kernel(float* __restrict__ chunk_S, float* __restrict__ chunk_n
 
 using namespace imparo;
 
-template <int DMAX, int NW>
+template <int DMAX, int NW, int SPLIT>
 static int mlstm_launch_nw(const MlstmCols& c, float* S, float* n, float* m, const int* item_row_start, const int* item_slot, int n_slots,
                            int n_items, int n_tok, float* out, int heads, int dim, int vdim, int chunk, float* chunk_S, float* chunk_n,
                            float* chunk_mb, int* status, cudaStream_t stream) {
     const int vblocks = (vdim + 31) / 32;
-    const int zb = (vblocks + NW - 1) / NW;
+    const int zb = (vdim + NW * (32 / SPLIT) - 1) / (NW * (32 / SPLIT));
     if (chunk <= 0) {
-        launch(mlstm_recurrent_kernel<DMAX, NW>, dim3(n_items, heads, zb), dim3(NW * 32), 0, stream, c, S, n, m, item_row_start, item_slot,
+        launch(mlstm_recurrent_kernel<DMAX, NW, SPLIT>, dim3(n_items, heads, zb), dim3(NW * 32), 0, stream, c, S, n, m, item_row_start, item_slot,
                n_slots, out, heads, dim, vdim, vblocks, status);
         IMPARO_CHECK_LAUNCH();
         return 0;
     }
     const int most = n_tok / chunk + n_items;
-    launch(mlstm_chunk_kernel<DMAX, NW, false>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
+    launch(mlstm_chunk_kernel<DMAX, NW, SPLIT, false>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
            item_row_start, n_items, chunk, (float*)nullptr, heads, dim, vdim, vblocks, item_slot, n_slots, m);
     IMPARO_CHECK_LAUNCH();
     const int entries = dim * vdim + vblocks * dim;
     launch(mlstm_chunk_scan_kernel, dim3(n_items, heads, (entries + 255) / 256), dim3(256), 0, stream, chunk_S, chunk_n, chunk_mb, S, n,
            (const float*)m, item_row_start, item_slot, n_slots, chunk, heads, dim, vdim, vblocks, status);
     IMPARO_CHECK_LAUNCH();
-    launch(mlstm_chunk_kernel<DMAX, NW, true>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
+    launch(mlstm_chunk_kernel<DMAX, NW, SPLIT, true>, dim3(most, heads, zb), dim3(NW * 32), 0, stream, c, chunk_S, chunk_n, chunk_mb,
            item_row_start, n_items, chunk, out, heads, dim, vdim, vblocks, item_slot, n_slots, m);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
 
-// the warps of a CTA share the staged keys and queries: as many as the head has blocks of value columns, up to four
+// the warps of a CTA share the staged keys and queries: as many as the head's value columns fill, up to four; key sizes above 64
+// are split over two lanes per column
 template <int DMAX>
 static int mlstm_launch(const MlstmCols& c, float* S, float* n, float* m, const int* item_row_start, const int* item_slot, int n_slots,
                         int n_items, int n_tok, float* out, int heads, int dim, int vdim, int chunk, float* chunk_S, float* chunk_n,
                         float* chunk_mb, int* status, cudaStream_t stream) {
-    const int vblocks = (vdim + 31) / 32;
-    if (vblocks >= 3)
-        return mlstm_launch_nw<DMAX, 4>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
-                                        chunk_S, chunk_n, chunk_mb, status, stream);
-    if (vblocks == 2)
-        return mlstm_launch_nw<DMAX, 2>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
-                                        chunk_S, chunk_n, chunk_mb, status, stream);
-    return mlstm_launch_nw<DMAX, 1>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
-                                    chunk_S, chunk_n, chunk_mb, status, stream);
+    constexpr int SPLIT = DMAX > 64 ? 2 : 1;
+    const int wblocks = (vdim + 32 / SPLIT - 1) / (32 / SPLIT);          // warps a head's value columns fill
+    if (wblocks >= 3)
+        return mlstm_launch_nw<DMAX, 4, SPLIT>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                               chunk_S, chunk_n, chunk_mb, status, stream);
+    if (wblocks == 2)
+        return mlstm_launch_nw<DMAX, 2, SPLIT>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                               chunk_S, chunk_n, chunk_mb, status, stream);
+    return mlstm_launch_nw<DMAX, 1, SPLIT>(c, S, n, m, item_row_start, item_slot, n_slots, n_items, n_tok, out, heads, dim, vdim, chunk,
+                                           chunk_S, chunk_n, chunk_mb, status, stream);
 }
 
 // proj: float32 rows of `stride` floats with q and k (heads * dim each), v (heads * vdim) and the two gates' pre-activations

@@ -101,7 +101,8 @@ class MatrixMemory(Part):
             # follows the step's totals alone (tokens, requests), which are part of its shape
             vb = ops.mlstm_value_blocks(self.vdim)
             chunk = self.CHUNK
-            if (T // chunk + batch.n_items) * H * -(-vb // 4) < ops.sm_count():
+            per_cta = 128 if self.dim <= 64 else 64          # value columns a CTA of the recurrence covers
+            if (T // chunk + batch.n_items) * H * -(-self.vdim // per_cta) < ops.sm_count():
                 chunk //= 2
             most = T // chunk + batch.n_items
             scratch = (ws.get("mlstm_chunk_S", (most * H * self.dim * self.vdim,), torch.float32),
